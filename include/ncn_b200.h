@@ -1,0 +1,115 @@
+/* C ABI of the B200 NCN library (libncn_b200.so).
+ *
+ * Drop-in boundary for the reference's pybind11 extension `ncn_cuda_module`
+ * (ncn_cuda/ncn_cuda.cpp:3-32), whose two functions are
+ *   forward (X, Xa, W, alpha, activation, cache_dim, nhead, module_l) -> {Y, Ya}
+ *   backward(Y, Ya, dY, dYa, W, alpha, activation, cache_dim, nhead, module_l) -> {X, Xa, dX, dXa, dW}
+ * and for the Python stage loop above it (ncn_cuda/ncn_pytorch_wrapper_v2.py:107-144).
+ *
+ * Conventions
+ *  - every tensor is a contiguous [B, N, E] array on the current CUDA device, element type
+ *    `dtype` (NCN_F32 or NCN_BF16); weights and weight gradients are always fp32;
+ *  - W of one stage is [2E] = [Wi | Wj] (torch_ref/ncn_pytorch.py:60-61); W of a net is [L][2E];
+ *  - activation codes are the reference's (ncn_pytorch_wrapper_v2.py:111):
+ *    0 tanh, 1 relu, 2 sigmoid, anything else (-1) linear;
+ *  - the caller owns every buffer; nothing is allocated, freed or memset by the library
+ *    (unless a function says otherwise); every output element is written exactly once;
+ *  - work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns without
+ *    synchronising; arguments are validated first and a non-zero status means nothing was
+ *    enqueued;
+ *  - the weight gradient is returned already summed over batch and positions (the reference
+ *    returns a [B, N, 2E] buffer and lets the wrapper sum it, ncn_pytorch_wrapper_v2.py:48); the
+ *    sum runs in a fixed order, so it is bitwise reproducible for equal arguments on one device.
+ */
+#ifndef NCN_B200_H_
+#define NCN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { NCN_F32 = 0, NCN_BF16 = 1 };
+
+/* status codes */
+enum {
+  NCN_OK = 0,
+  NCN_ERR_SHAPE = 1,       /* n_cache does not divide N, n_head does not divide E, sizes <= 0 */
+  NCN_ERR_DTYPE = 2,       /* dtype is neither NCN_F32 nor NCN_BF16 */
+  NCN_ERR_ALIGN = 3,       /* a tensor pointer is not 16-byte aligned (fused path only) */
+  NCN_ERR_SMEM = 4,        /* the tile does not fit the shared memory of one SM */
+  NCN_ERR_UNSUPPORTED = 5, /* the fused all-stage path does not cover these arguments; use the per-stage calls */
+  NCN_ERR_WORKSPACE = 6,   /* workspace missing or smaller than ncn_bwd_workspace_bytes() */
+  NCN_ERR_CUDA = 7,        /* a CUDA runtime call failed; see ncn_last_cuda_error() */
+  NCN_ERR_NULL = 8,        /* a required pointer is null */
+  NCN_ERR_DEVICE_WAIT = 9  /* (ncn_device_status) a kernel gave up a bounded wait on a copy */
+};
+
+/* flags of the net calls */
+enum {
+  NCN_RESIDUAL = 1,  /* forward: y = x + net(x, xa).x ; backward: dx = dx_net + dy */
+  NCN_RECOMPUTE = 2  /* backward: s0/s1 are the net INPUT (x, xa); the forward is replayed in fp32.
+                        Required with bf16 storage and with NCN_RESIDUAL. */
+};
+
+/* One stage forward.  Replaces ncn_cuda_module.forward (ncn_cuda/ncn_cuda.cpp:30;
+ * ncn_cuda/ncn_fwd_cuda_kernel.cu:115-161); the step loop runs over the n_cache positions of a
+ * group as torch_ref/ncn_pytorch.py:74 does. */
+int ncn_stage_fwd(const void* x, const void* xa, const float* W, void* y, void* ya, int64_t B, int64_t N, int64_t E,
+                  int n_cache, int n_head, int module_l, double alpha, int activation, int dtype, void* stream);
+
+/* One stage backward from the stage OUTPUT (reversible reconstruction).  Replaces
+ * ncn_cuda_module.backward (ncn_cuda/ncn_cuda.cpp:31; ncn_cuda/ncn_bwd_cuda_kernel.cu:232-288)
+ * plus the wrapper's torch.sum over the dW buffer (ncn_pytorch_wrapper_v2.py:48).
+ * x_rec / xa_rec (the rebuilt stage input) may be null.  dW is [2E] fp32.
+ * workspace: device memory of at least ncn_bwd_workspace_bytes(...) bytes, fully overwritten. */
+int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
+                  void* x_rec, void* xa_rec, float* dW, void* workspace, size_t workspace_bytes, int64_t B, int64_t N,
+                  int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation, int dtype,
+                  void* stream);
+
+/* All L stages (module_l = first_module .. first_module+L-1) in one kernel.  Replaces the stage
+ * loops NCNNetCuda.forward / NCNNetTestCuda.forward (ncn_pytorch_wrapper_v2.py:114-117,132-144).
+ * ckpt (may be null): fp32 buffer of ncn_ckpt_bytes(...) bytes that receives the state after every
+ * ckpt_every-th stage, for ncn_net_bwd.  Returns NCN_ERR_UNSUPPORTED where only the per-stage calls
+ * apply (E != 1, n_cache not in {2,4,8,16}, N not a multiple of 4 (fp32) / 8 (bf16)). */
+int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya, float* ckpt, int ckpt_every,
+                int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module, int L, double alpha,
+                int activation, int dtype, int flags, void* stream);
+
+/* Backward of ncn_net_fwd in one kernel.  s0/s1 are the net OUTPUT (y, ya) — every stage input is
+ * rebuilt by the reversible inverse, restarting at each stored checkpoint — or, with NCN_RECOMPUTE,
+ * the net INPUT.  dW is [L][2E] fp32; with dw_accumulate != 0 the result is added to it.
+ * x_rec / xa_rec may be null. */
+int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
+                void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, void* workspace,
+                size_t workspace_bytes, int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module,
+                int L, double alpha, int activation, int dtype, int flags, int dw_accumulate, void* stream);
+
+/* 1 if ncn_net_fwd / ncn_net_bwd cover these arguments on the current device, else 0. */
+int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype, int flags,
+                      int ckpt_every);
+
+/* Workspace (bytes) that ncn_stage_bwd (L = 1) or ncn_net_bwd needs for these arguments. */
+size_t ncn_bwd_workspace_bytes(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype);
+
+/* Size (bytes) of the checkpoint buffer: ((L-1)/ckpt_every) states of 2 x [B, N, E] fp32. */
+size_t ncn_ckpt_bytes(int64_t B, int64_t N, int64_t E, int L, int ckpt_every);
+
+/* Reads and clears the device status word (synchronises the device): NCN_OK, or
+ * NCN_ERR_DEVICE_WAIT if a kernel abandoned a bounded wait since the last call. */
+int ncn_device_status(void);
+
+/* Text for a status code; the last CUDA error string seen by this thread. */
+const char* ncn_status_string(int status);
+const char* ncn_last_cuda_error(void);
+
+/* Library version (major*100 + minor). */
+int ncn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NCN_B200_H_ */

@@ -1,0 +1,446 @@
+// C ABI of the NCN library: argument validation, launch planning, kernel launches.
+// Declarations and the reference interfaces they replace are in include/ncn_b200.h.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/ncn_b200.h"
+#include "ncn_generic.cuh"
+#include "ncn_rows_launch.h"
+
+namespace ncn {
+
+__device__ int g_status_word = 0;
+
+static thread_local char tl_cuda_err[256] = "";
+
+static int cuda_fail(cudaError_t e) {
+  std::snprintf(tl_cuda_err, sizeof(tl_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+  return NCN_ERR_CUDA;
+}
+
+struct DevInfo {
+  int dev = -1, sms = 0, smem_optin = 0;
+  int* status = nullptr;
+};
+
+// Per-device facts, looked up once per device and cached (the table is tiny and written
+// idempotently, so a race between two first calls is harmless).
+static int get_dev(DevInfo& out) {
+  static DevInfo table[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return NCN_ERR_CUDA;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    DevInfo d;
+    d.dev = dev;
+    if ((e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return cuda_fail(e);
+    if ((e = cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess)
+      return cuda_fail(e);
+    if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_status_word)) != cudaSuccess)
+      return cuda_fail(e);
+    table[dev] = d;
+    ready[dev].store(1, std::memory_order_release);
+  }
+  out = table[dev];
+  return NCN_OK;
+}
+
+static int map_act(int code) {
+  switch (code) {
+    case 0: return ACT_TANH;
+    case 1: return ACT_RELU;
+    case 2: return ACT_SIGMOID;
+    default: return ACT_LINEAR;
+  }
+}
+
+static inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static bool rows_shape_ok(int64_t N, int64_t E, int n, int C, int dtype) {
+  if (E != 1 || C != 1) return false;
+  if (!(n == 2 || n == 4 || n == 8 || n == 16)) return false;
+  const int64_t quantum = dtype == DT_BF16 ? 8 : 4;  // 16-byte rows for the bulk copies
+  if (N % quantum != 0) return false;
+  if (N / n > (1 << 24)) return false;
+  return true;
+}
+
+struct Plan {
+  int threads = 0, R = 0, nbuf = 0, grid = 0;
+  size_t smem = 0;
+  uint32_t off_in[2] = {0, 0}, off_work = 0, off_out = 0, off_ckpt = kNoOff, off_red = 0, off_w = 0, off_bar = 0;
+  uint32_t n_ckpt_slots = 0;
+  long long tiles = 0;
+};
+
+typedef cudaError_t (*RowsLaunchFn)(int, int, const RowsParams&, int, int, size_t, cudaStream_t, int*);
+
+static RowsLaunchFn rows_fn(int n, bool bwd) {
+  switch (n) {
+    case 2: return bwd ? launch_rows_bwd_n2 : launch_rows_fwd_n2;
+    case 4: return bwd ? launch_rows_bwd_n4 : launch_rows_fwd_n4;
+    case 8: return bwd ? launch_rows_bwd_n8 : launch_rows_fwd_n8;
+    case 16: return bwd ? launch_rows_bwd_n16 : launch_rows_fwd_n16;
+    default: return nullptr;
+  }
+}
+
+// Lay the tile out in shared memory.  Preference: two input buffers (prefetch of the next tile
+// starts a whole tile early) > checkpoints staged in shared memory > one input buffer.
+static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
+                     const DevInfo& dev, int act, Plan& pl) {
+  const int w = dtype == DT_BF16 ? 2 : 4;
+  const int m = N / n;
+  const int maxT = rows_max_threads(n, bwd);
+  const bool recompute = (flags & F_RECOMPUTE) != 0;
+  if (recompute) n_ck = 0;
+  int R = m >= maxT ? 1 : maxT / m;
+  if ((int64_t)R > B) R = (int)B;
+  const uint32_t limit = (uint32_t)dev.smem_optin;
+
+  auto layout = [&](int R_, int nbuf, int slots, Plan& p) -> bool {
+    const int threads = (int)align_up((uint32_t)((int64_t)R_ * m < maxT ? R_ * m : maxT), 32);
+    const int nwarp = threads / 32;
+    const uint64_t RN = (uint64_t)R_ * N;
+    const uint64_t in_b = (bwd ? 4 : 2) * RN * w;
+    const bool need_work = bwd ? (L > 1 || recompute) : (L > 1);
+    const uint64_t work_b = need_work ? (bwd ? 4 : 2) * RN * 4 : 0;
+    const uint64_t out_b = (bwd ? (want_rec ? 4 : 2) : 2) * RN * w;
+    const uint64_t ck_b = (uint64_t)slots * 2 * RN * 4;
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) { uint64_t o = off; off = (off + bytes + 127) / 128 * 128; return (uint32_t)o; };
+    p.off_in[0] = take(in_b);
+    p.off_in[1] = nbuf == 2 ? take(in_b) : p.off_in[0];
+    p.off_work = take(work_b);
+    p.off_out = take(out_b);
+    p.off_ckpt = slots ? take(ck_b) : kNoOff;
+    p.off_red = take(bwd ? (uint64_t)2 * L * nwarp * 4 : 0);
+    p.off_w = take((uint64_t)2 * L * 4);
+    p.off_bar = take(32);
+    if (off > limit) return false;
+    p.threads = threads;
+    p.R = R_;
+    p.nbuf = nbuf;
+    p.n_ckpt_slots = (uint32_t)slots;
+    p.smem = (size_t)off;
+    return true;
+  };
+
+  bool ok = false;
+  for (; R >= 1 && !ok; R = (R > 1 ? R / 2 : 0)) {
+    if (bwd && n_ck > 0) {
+      ok = layout(R, 1, n_ck, pl) || layout(R, 1, 0, pl);
+    } else {
+      ok = layout(R, 2, 0, pl) || layout(R, 1, 0, pl);
+    }
+    if (ok) break;
+  }
+  if (!ok) return NCN_ERR_SMEM;
+  pl.tiles = (B + pl.R - 1) / pl.R;
+  int occ = 0;
+  RowsParams dummy{};
+  cudaError_t e = rows_fn(n, bwd)(act, dtype, dummy, 0, pl.threads, pl.smem, nullptr, &occ);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (occ < 1) return NCN_ERR_SMEM;
+  if (occ > 32) occ = 32;
+  long long grid = (long long)dev.sms * occ;
+  if (grid > pl.tiles) grid = pl.tiles;
+  pl.grid = (int)grid;
+  return NCN_OK;
+}
+
+static void fill_offsets(RowsParams& p, const Plan& pl) {
+  p.off_in[0] = pl.off_in[0];
+  p.off_in[1] = pl.off_in[1];
+  p.off_work = pl.off_work;
+  p.off_out = pl.off_out;
+  p.off_ckpt = pl.off_ckpt;
+  p.off_red = pl.off_red;
+  p.off_w = pl.off_w;
+  p.off_bar = pl.off_bar;
+  p.n_ckpt_slots = pl.n_ckpt_slots;
+  p.R = pl.R;
+  p.nbuf = pl.nbuf;
+  p.tiles = pl.tiles;
+}
+
+static int check_common(int64_t B, int64_t N, int64_t E, int n, int C, int dtype) {
+  if (B <= 0 || N <= 0 || E <= 0 || n <= 0 || C <= 0) return NCN_ERR_SHAPE;
+  if (N % n != 0 || E % C != 0) return NCN_ERR_SHAPE;
+  if (N > (1LL << 30) || E > (1LL << 24)) return NCN_ERR_SHAPE;
+  if (dtype != DT_F32 && dtype != DT_BF16) return NCN_ERR_DTYPE;
+  return NCN_OK;
+}
+
+static int reduce_dw(const float* partials, float* dW, int rows, int cols, int accumulate, cudaStream_t st) {
+  const int warps = 4;
+  dw_reduce_kernel<<<(cols + warps - 1) / warps, warps * 32, 0, st>>>(partials, dW, rows, cols, accumulate);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? NCN_OK : cuda_fail(e);
+}
+
+// ---- generic per-stage launches
+struct GenericPlan {
+  int warps = 0, grid = 0;
+  size_t smem = 0;
+  uint32_t warp_floats = 0;
+};
+
+template <typename K>
+static int plan_generic(K kernel, bool bwd, int64_t groups, int n, int d, int E, const DevInfo& dev, GenericPlan& g) {
+  const int pitch = d | 1;
+  const uint64_t wf = bwd ? (uint64_t)5 * n * pitch + d + 2 * n + 2 * E : (uint64_t)2 * n * pitch + d + n;
+  int warps = 8;
+  while (warps > 1 && wf * 4 * warps > (uint64_t)dev.smem_optin) warps /= 2;
+  if (wf * 4 * warps > (uint64_t)dev.smem_optin) return NCN_ERR_SMEM;
+  g.warps = warps;
+  g.warp_floats = (uint32_t)wf;
+  g.smem = (size_t)(wf * 4 * warps);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int occ = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, warps * 32, g.smem);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (occ < 1) return NCN_ERR_SMEM;
+  if (occ > 8) occ = 8;
+  long long grid = (groups + warps - 1) / warps;
+  if (grid > (long long)dev.sms * occ) grid = (long long)dev.sms * occ;
+  g.grid = (int)grid;
+  return NCN_OK;
+}
+
+static void fill_stage(StageParams& p, int64_t B, int64_t N, int64_t E, int n, int C, int module_l, double alpha) {
+  p.B = B;
+  p.N = (int)N;
+  p.E = (int)E;
+  p.C = C;
+  p.d = (int)(E / C);
+  p.n = n;
+  p.m = (int)(N / n);
+  p.groups = B * C * (N / n);
+  p.stride = stage_stride(module_l, p.m);
+  p.pitch = p.d | 1;
+  int sh = 0;
+  while (sh < 5 && (2 << sh) <= p.d) ++sh;
+  p.ld_shift = sh;
+  p.alpha = (float)alpha;
+  p.oma = (float)(1.0 - alpha);
+}
+
+static size_t workspace_floats(const DevInfo& dev, int64_t E, int L) {
+  return (size_t)dev.sms * 32 * 2 * (size_t)E * (size_t)(L < 1 ? 1 : L);
+}
+
+}  // namespace ncn
+
+using namespace ncn;
+
+extern "C" {
+
+int ncn_version(void) { return 100; }
+
+const char* ncn_status_string(int s) {
+  switch (s) {
+    case NCN_OK: return "ok";
+    case NCN_ERR_SHAPE: return "bad shape: n_cache must divide N, n_head must divide E, all sizes positive";
+    case NCN_ERR_DTYPE: return "unsupported dtype (fp32 and bf16 only)";
+    case NCN_ERR_ALIGN: return "tensor pointer not 16-byte aligned";
+    case NCN_ERR_SMEM: return "tile does not fit in shared memory";
+    case NCN_ERR_UNSUPPORTED: return "fused all-stage path does not cover these arguments";
+    case NCN_ERR_WORKSPACE: return "workspace missing or too small";
+    case NCN_ERR_CUDA: return "CUDA runtime error";
+    case NCN_ERR_NULL: return "null pointer";
+    case NCN_ERR_DEVICE_WAIT: return "a kernel abandoned a bounded wait on an asynchronous copy";
+    default: return "unknown status";
+  }
+}
+
+const char* ncn_last_cuda_error(void) { return tl_cuda_err; }
+
+int ncn_device_status(void) {
+  int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int));
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (v != 0) {
+    e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e);
+    return NCN_ERR_DEVICE_WAIT;
+  }
+  return NCN_OK;
+}
+
+size_t ncn_bwd_workspace_bytes(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype) {
+  (void)B; (void)N; (void)n_cache; (void)n_head; (void)dtype;
+  DevInfo dev;
+  if (get_dev(dev) != NCN_OK) return 0;
+  return workspace_floats(dev, E, L) * sizeof(float);
+}
+
+size_t ncn_ckpt_bytes(int64_t B, int64_t N, int64_t E, int L, int ckpt_every) {
+  if (ckpt_every <= 0 || L <= 1) return 0;
+  return (size_t)((L - 1) / ckpt_every) * 2 * (size_t)B * (size_t)N * (size_t)E * sizeof(float);
+}
+
+int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype, int flags,
+                      int ckpt_every) {
+  if (check_common(B, N, E, n_cache, n_head, dtype) != NCN_OK || L < 1) return 0;
+  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return 0;
+  DevInfo dev;
+  if (get_dev(dev) != NCN_OK) return 0;
+  Plan pl;
+  const int n_ck = ckpt_every > 0 ? (L - 1) / ckpt_every : 0;
+  if (plan_rows(false, B, (int)N, n_cache, L, dtype, flags, 0, false, dev, ACT_TANH, pl) != NCN_OK) return 0;
+  if (plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, true, dev, ACT_TANH, pl) != NCN_OK) return 0;
+  return 1;
+}
+
+int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya, float* ckpt, int ckpt_every,
+                int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module, int L, double alpha,
+                int activation, int dtype, int flags, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
+  if (!x || !xa || !W || !y || !ya) return NCN_ERR_NULL;
+  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(xa) || !aligned16(y) || !aligned16(ya) || (ckpt && !aligned16(ckpt)))
+    return NCN_ERR_ALIGN;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  const int act = map_act(activation);
+  Plan pl;
+  if ((rc = plan_rows(false, B, (int)N, n_cache, L, dtype, flags, 0, false, dev, act, pl)) != NCN_OK) return rc;
+  RowsParams p{};
+  p.in[0] = x; p.in[1] = xa;
+  p.out[0] = y; p.out[1] = ya;
+  p.ckpt = (ckpt && ckpt_every > 0 && (L - 1) / ckpt_every > 0) ? ckpt : nullptr;
+  p.ckpt_every = ckpt_every;
+  p.W = W;
+  p.status = dev.status;
+  p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
+  p.flags = flags & F_RESIDUAL;
+  p.alpha = (float)alpha;
+  p.oma = (float)(1.0 - alpha);
+  fill_offsets(p, pl);
+  cudaError_t e = rows_fn(n_cache, false)(act, dtype, p, pl.grid, pl.threads, pl.smem, (cudaStream_t)stream, nullptr);
+  return e == cudaSuccess ? NCN_OK : cuda_fail(e);
+}
+
+int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
+                void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, void* workspace,
+                size_t workspace_bytes, int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module,
+                int L, double alpha, int activation, int dtype, int flags, int dw_accumulate, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
+  if (!s0 || !s1 || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
+  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
+  if ((flags & F_RESIDUAL) && !(flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
+  if (!aligned16(s0) || !aligned16(s1) || !aligned16(dy) || !aligned16(dya) || !aligned16(dx) || !aligned16(dxa) ||
+      (x_rec && (!aligned16(x_rec) || !aligned16(xa_rec))) || (ckpt && !aligned16(ckpt)))
+    return NCN_ERR_ALIGN;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  if (!workspace || workspace_bytes < workspace_floats(dev, E, L) * sizeof(float)) return NCN_ERR_WORKSPACE;
+  const int act = map_act(activation);
+  const bool use_ck = ckpt && ckpt_every > 0 && !(flags & F_RECOMPUTE) && (L - 1) / ckpt_every > 0;
+  const int n_ck = use_ck ? (L - 1) / ckpt_every : 0;
+  Plan pl;
+  if ((rc = plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, x_rec != nullptr, dev, act, pl)) != NCN_OK)
+    return rc;
+  RowsParams p{};
+  p.in[0] = s0; p.in[1] = s1; p.in[2] = dy; p.in[3] = dya;
+  p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
+  p.ckpt = use_ck ? const_cast<float*>(ckpt) : nullptr;
+  p.ckpt_every = ckpt_every;
+  p.W = W;
+  p.partials = static_cast<float*>(workspace);
+  p.status = dev.status;
+  p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
+  p.flags = flags & (F_RESIDUAL | F_RECOMPUTE);
+  p.alpha = (float)alpha;
+  p.oma = (float)(1.0 - alpha);
+  fill_offsets(p, pl);
+  cudaError_t e = rows_fn(n_cache, true)(act, dtype, p, pl.grid, pl.threads, pl.smem, (cudaStream_t)stream, nullptr);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return reduce_dw(p.partials, dW, pl.grid, 2 * L, dw_accumulate, (cudaStream_t)stream);
+}
+
+int ncn_stage_fwd(const void* x, const void* xa, const float* W, void* y, void* ya, int64_t B, int64_t N, int64_t E,
+                  int n_cache, int n_head, int module_l, double alpha, int activation, int dtype, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!x || !xa || !W || !y || !ya) return NCN_ERR_NULL;
+  if (rows_shape_ok(N, E, n_cache, n_head, dtype) && aligned16(x) && aligned16(xa) && aligned16(y) && aligned16(ya)) {
+    rc = ncn_net_fwd(x, xa, W, y, ya, nullptr, 0, B, N, E, n_cache, n_head, module_l, 1, alpha, activation, dtype, 0,
+                     stream);
+    if (rc != NCN_ERR_SMEM) return rc;
+  }
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  StageParams p{};
+  fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
+  p.in[0] = x; p.in[1] = xa;
+  p.out[0] = y; p.out[1] = ya;
+  p.W = W;
+  GenericPlan g;
+  const int act = map_act(activation);
+  if (dtype == DT_BF16) {
+    if ((rc = plan_generic(stage_fwd_kernel<__nv_bfloat16>, false, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_fwd_kernel<__nv_bfloat16><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  } else {
+    if ((rc = plan_generic(stage_fwd_kernel<float>, false, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_fwd_kernel<float><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? NCN_OK : cuda_fail(e);
+}
+
+int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
+                  void* x_rec, void* xa_rec, float* dW, void* workspace, size_t workspace_bytes, int64_t B, int64_t N,
+                  int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation, int dtype,
+                  void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!y || !ya || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  if (!workspace || workspace_bytes < workspace_floats(dev, E, 1) * sizeof(float)) return NCN_ERR_WORKSPACE;
+  if (rows_shape_ok(N, E, n_cache, n_head, dtype) && aligned16(y) && aligned16(ya) && aligned16(dy) && aligned16(dya) &&
+      aligned16(dx) && aligned16(dxa) && (!x_rec || (aligned16(x_rec) && aligned16(xa_rec)))) {
+    rc = ncn_net_bwd(y, ya, dy, dya, W, dx, dxa, x_rec, xa_rec, dW, nullptr, 0, workspace, workspace_bytes, B, N, E,
+                     n_cache, n_head, module_l, 1, alpha, activation, dtype, 0, 0, stream);
+    if (rc != NCN_ERR_SMEM) return rc;
+  }
+  StageParams p{};
+  fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
+  p.in[0] = y; p.in[1] = ya; p.in[2] = dy; p.in[3] = dya;
+  p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
+  p.W = W;
+  p.partials = static_cast<float*>(workspace);
+  GenericPlan g;
+  const int act = map_act(activation);
+  if (dtype == DT_BF16) {
+    if ((rc = plan_generic(stage_bwd_kernel<__nv_bfloat16>, true, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_bwd_kernel<__nv_bfloat16><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  } else {
+    if ((rc = plan_generic(stage_bwd_kernel<float>, true, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_bwd_kernel<float><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return reduce_dw(p.partials, dW, g.grid, 2 * (int)E, 0, (cudaStream_t)stream);
+}
+
+}  // extern "C"

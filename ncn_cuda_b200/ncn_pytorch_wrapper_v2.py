@@ -1,0 +1,195 @@
+"""The reference's CUDA operator surface, backed by the sm_100a kernels.
+
+Mirrors ncn_cuda/ncn_pytorch_wrapper_v2.py of erlandbo/ncn-cuda: `NCNFunction` (:9-50),
+`fused_ncn_cuda_v2` (:53-73), `NCNModuleCuda` (:77-103), `NCNNetCuda` (:107-117) and
+`NCNNetTestCuda` (:121-144) keep their names, argument order, weight layout ([2*embed_dim] =
+[Wi | Wj] per stage, `state_dict` key `ncn_modules.<l>.weight`) and stage ordering
+(module_l = 0, 1, 2, ...).  Differences, all inside the boundary:
+
+* the nets run every stage in ONE kernel per direction (`NCNNetFunction`) whenever the
+  fused path covers the shape (one feature per position); otherwise they loop over
+  `NCNFunction` stage by stage exactly as the reference does;
+* the weight gradient comes back reduced from the library (no [B, N, 2E] buffer);
+* `NCNModuleCuda.forward` passes n_cache / n_head by keyword — the reference passes them
+  swapped (ncn_pytorch_wrapper_v2.py:92-102).
+"""
+from __future__ import annotations
+
+import math
+from typing import Sequence, Tuple
+
+import torch
+from torch import nn
+
+from . import ops
+
+# Longest chain of steps rebuilt by the reversible inverse before the backward restarts from a
+# stored state.  Each inverse step grows earlier rounding by 1/0.9; 16 steps keep fp32
+# gradients at the accuracy of plain autograd, 24-32 steps reach a few 1e-6.
+MAX_INVERSE_STEPS = 16
+
+
+class NCNFunction(torch.autograd.Function):
+    """One stage.  Saves only the stage OUTPUT; backward rebuilds the input by the
+    reversible inverse (ncn_cuda/ncn_pytorch_wrapper_v2.py:9-50)."""
+
+    @staticmethod
+    def forward(ctx, x, xa, W, alpha, activation, n_cache, n_head, module_l):
+        yi, ya = ops.stage_fwd(x, xa, W, alpha, activation, n_cache, n_head, module_l)
+        ctx.save_for_backward(yi, ya, W)
+        ctx.alpha = alpha
+        ctx.activation = activation
+        ctx.n_cache = n_cache
+        ctx.n_head = n_head
+        ctx.module_l = module_l
+        return yi, ya
+
+    @staticmethod
+    def backward(ctx, dyi, dya):
+        (yi, ya, W) = ctx.saved_tensors
+        dx, dxa, dW = ops.stage_bwd(
+            yi, ya, dyi, dya, W, ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l
+        )
+        return dx, dxa, dW.to(W.dtype), None, None, None, None, None
+
+
+def fused_ncn_cuda_v2(
+    x: torch.Tensor,
+    xa: torch.Tensor,
+    W: torch.Tensor,
+    alpha: float,
+    activation: int,
+    n_cache: int,
+    n_head: int,
+    module_l: int,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    yi, ya = NCNFunction.apply(x, xa, W, alpha, activation, n_cache, n_head, module_l)
+    return yi, ya
+
+
+def plan_backward(dtype, n_cache: int, num_modules: int, residual: bool, backward_mode: str):
+    """-> (recompute, ckpt_every) for a fused net.
+
+    "invert"      rebuild everything from the net output (the reference's reversible backward
+                  applied across all stages; nothing but the output is stored)
+    "checkpoint"  as invert, but the forward also stores the state every few stages so that no
+                  inverse chain exceeds MAX_INVERSE_STEPS steps
+    "recompute"   store the net input and replay the forward in fp32 inside the backward kernel
+    "auto"        recompute for bf16 storage and residual layers, else checkpoint
+    """
+    if backward_mode not in ("auto", "invert", "checkpoint", "recompute"):
+        raise ValueError(f"unknown backward_mode {backward_mode!r}")
+    if backward_mode == "auto":
+        backward_mode = "recompute" if (dtype != torch.float32 or residual) else "checkpoint"
+    if residual and backward_mode != "recompute":
+        raise ValueError("residual layers need backward_mode='recompute'")
+    if backward_mode == "recompute":
+        return True, 0
+    if backward_mode == "invert":
+        return False, 0
+    every = max(1, MAX_INVERSE_STEPS // n_cache)
+    return False, (every if num_modules > every else 0)
+
+
+class NCNNetFunction(torch.autograd.Function):
+    """All stages of a net in one forward and one backward kernel.  W: [L, 2E]."""
+
+    @staticmethod
+    def forward(ctx, x, xa, W, alpha, activation, n_cache, n_head, first_module, backward_mode, residual):
+        recompute, every = plan_backward(x.dtype, n_cache, W.shape[0], residual, backward_mode)
+        y, ya, ckpt = ops.net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module, every, residual)
+        if recompute:
+            ctx.save_for_backward(x, xa, W)
+        else:
+            ctx.save_for_backward(y, ya, W)
+        ctx.ckpt = ckpt
+        ctx.cfg = (alpha, activation, n_cache, n_head, first_module, every, recompute, residual)
+        return y, ya
+
+    @staticmethod
+    def backward(ctx, dy, dya):
+        s0, s1, W = ctx.saved_tensors
+        alpha, activation, n_cache, n_head, first_module, every, recompute, residual = ctx.cfg
+        dx, dxa, dW = ops.net_bwd(
+            s0, s1, dy, dya, W, alpha, activation, n_cache, n_head, first_module,
+            ckpt=ctx.ckpt, ckpt_every=every, recompute=recompute, residual=residual,
+        )
+        ctx.ckpt = None
+        return dx, dxa, dW.to(W.dtype), None, None, None, None, None, None, None
+
+
+def fused_ncn_net(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, backward_mode="auto", residual=False):
+    """Functional form of NCNNetFunction.  W: [L, 2E] (stage l uses W[l])."""
+    return NCNNetFunction.apply(x, xa, W, alpha, activation, n_cache, n_head, first_module, backward_mode, residual)
+
+
+def _net_forward(x, xa, weights: Sequence[torch.Tensor], alpha, activation_nr, n_cache, n_head, backward_mode):
+    """Shared by the two net modules: fused when the library covers the shape, else stage by stage."""
+    L = len(weights)
+    if L > 0 and x.is_cuda and ops.net_supported(x, n_cache, n_head, L):
+        W = torch.stack([w.reshape(-1) for w in weights])
+        return fused_ncn_net(x, xa, W, alpha, activation_nr, n_cache, n_head, 0, backward_mode)
+    for module_nr in range(L):
+        x, xa = fused_ncn_cuda_v2(x, xa, weights[module_nr], alpha, activation_nr, n_cache, n_head, module_nr)
+    return x, xa
+
+
+class NCNModuleCuda(nn.Module):
+    def __init__(self, alpha, activation, n_cache, n_head, module_nr, embed_dim):
+        super().__init__()
+        self.alpha = alpha
+        self.activation = activation
+        self.n_cache = n_cache
+        self.n_head = n_head
+        self.module_nr = module_nr
+        self.embed_dim = embed_dim
+        self.weight = torch.nn.Parameter(
+            torch.ones(2 * embed_dim).normal_(mean=0.0, std=1 / (2.0 * embed_dim)), requires_grad=True
+        )
+
+    def reset_parameters(self):
+        stdv = 1.0 / math.sqrt(self.embed_dim)
+        for weight in self.parameters():
+            weight.data.uniform_(-stdv, +stdv)
+
+    def forward(self, x, xa):
+        return fused_ncn_cuda_v2(
+            x, xa, self.weight, self.alpha, self.activation,
+            n_cache=self.n_cache, n_head=self.n_head, module_l=self.module_nr,
+        )
+
+
+class NCNNetCuda(nn.Module):
+    def __init__(self, alpha, activation, n_cache, n_head, num_modules, embed_dim, backward_mode="auto"):
+        super().__init__()
+        self.num_modules = num_modules
+        self.alpha = alpha
+        self.n_cache = n_cache
+        self.n_head = n_head
+        self.backward_mode = backward_mode
+        self.activation_nr = ops.ACTIVATION_CODES[activation]
+        self.ncn_modules = nn.ModuleList(
+            [NCNModuleCuda(alpha, self.activation_nr, n_cache, n_head, module_nr, embed_dim) for module_nr in range(num_modules)]
+        )
+
+    def forward(self, x, xa):
+        weights = [mod.weight for mod in self.ncn_modules]
+        return _net_forward(x, xa, weights, self.alpha, self.activation_nr, self.n_cache, self.n_head, self.backward_mode)
+
+
+class NCNNetTestCuda(nn.Module):
+    def __init__(self, alpha, activation, n_cache, n_head, num_modules, weights, backward_mode="auto"):
+        super().__init__()
+        self.num_modules = num_modules
+        self.alpha = alpha
+        self.activation_nr = ops.ACTIVATION_CODES[activation]
+        self.n_cache = n_cache
+        self.n_head = n_head
+        self.weights = weights
+        self.backward_mode = backward_mode
+
+    def forward(self, x, xa):
+        return _net_forward(
+            x, xa, list(self.weights[: self.num_modules]), self.alpha, self.activation_nr, self.n_cache, self.n_head,
+            self.backward_mode,
+        )

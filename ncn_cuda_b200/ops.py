@@ -1,0 +1,176 @@
+"""Tensor-level calls into the C ABI (include/ncn_b200.h).
+
+torch is used for device memory and streams only; every function here launches
+kernels of libncn_b200.so on the current stream and returns torch tensors.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import NCN_BF16, NCN_F32, NCN_RECOMPUTE, NCN_RESIDUAL
+
+# activation vocabulary of the reference's CUDA wrapper (ncn_cuda/ncn_pytorch_wrapper_v2.py:111)
+ACTIVATION_CODES = {"tanh": 0, "relu": 1, "sigmoid": 2, "linear": -1}
+
+_workspaces = {}
+
+
+def activation_code(activation) -> int:
+    if isinstance(activation, str):
+        return ACTIVATION_CODES[activation]
+    return int(activation)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return NCN_F32
+    if t.dtype == torch.bfloat16:
+        return NCN_BF16
+    raise TypeError(f"NCN kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _check_inputs(*ts: torch.Tensor) -> None:
+    first = ts[0]
+    if not first.is_cuda:
+        raise RuntimeError("NCN kernels run on CUDA tensors only; there is no CPU path in this package")
+    if first.dim() != 3:
+        raise ValueError("expected [B, N, E] tensors")
+    for t in ts[1:]:
+        if t.shape != first.shape or t.dtype != first.dtype or t.device != first.device:
+            raise ValueError("x, xa (and the cotangents) must agree in shape, dtype and device")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _weights(W: torch.Tensor, numel: int, device) -> torch.Tensor:
+    W = W.detach()
+    if W.dtype != torch.float32 or not W.is_contiguous() or W.device != device:
+        W = W.to(device=device, dtype=torch.float32).contiguous()
+    if W.numel() != numel:
+        raise ValueError(f"weight has {W.numel()} elements, expected {numel}")
+    return W
+
+
+def _workspace(lib, device, B, N, E, n_cache, n_head, L, dt) -> torch.Tensor:
+    need = lib.ncn_bwd_workspace_bytes(B, N, E, n_cache, n_head, L, dt)
+    key = (device.index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def net_supported(x: torch.Tensor, n_cache: int, n_head: int, L: int, flags: int = 0, ckpt_every: int = 0) -> bool:
+    lib = _lib.load()
+    B, N, E = x.shape
+    with torch.cuda.device(x.device):
+        return bool(lib.ncn_net_supported(B, N, E, n_cache, n_head, L, _dtype_code(x), flags, ckpt_every))
+
+
+def stage_fwd(x, xa, W, alpha, activation, n_cache, n_head, module_l) -> Tuple[torch.Tensor, torch.Tensor]:
+    lib = _lib.load()
+    _check_inputs(x, xa)
+    x, xa = x.contiguous(), xa.contiguous()
+    B, N, E = x.shape
+    W = _weights(W, 2 * E, x.device)
+    y, ya = torch.empty_like(x), torch.empty_like(xa)
+    with torch.cuda.device(x.device):
+        rc = lib.ncn_stage_fwd(
+            x.data_ptr(), xa.data_ptr(), W.data_ptr(), y.data_ptr(), ya.data_ptr(), B, N, E, n_cache, n_head,
+            module_l, float(alpha), activation_code(activation), _dtype_code(x), _stream(),
+        )
+    _lib.check("ncn_stage_fwd", rc)
+    return y, ya
+
+
+def stage_bwd(y, ya, dy, dya, W, alpha, activation, n_cache, n_head, module_l, want_inputs: bool = False):
+    """Returns (dx, dxa, dW[2E]) and, with want_inputs, also the rebuilt (x, xa)."""
+    lib = _lib.load()
+    _check_inputs(y, ya, dy, dya)
+    y, ya, dy, dya = y.contiguous(), ya.contiguous(), dy.contiguous(), dya.contiguous()
+    B, N, E = y.shape
+    W = _weights(W, 2 * E, y.device)
+    dx, dxa = torch.empty_like(y), torch.empty_like(y)
+    xr = torch.empty_like(y) if want_inputs else None
+    xar = torch.empty_like(y) if want_inputs else None
+    dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
+    dt = _dtype_code(y)
+    with torch.cuda.device(y.device):
+        ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
+        rc = lib.ncn_stage_bwd(
+            y.data_ptr(), ya.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(), dxa.data_ptr(),
+            xr.data_ptr() if want_inputs else None, xar.data_ptr() if want_inputs else None, dW.data_ptr(),
+            ws.data_ptr(), ws.numel(), B, N, E, n_cache, n_head, module_l, float(alpha),
+            activation_code(activation), dt, _stream(),
+        )
+    _lib.check("ncn_stage_bwd", rc)
+    if want_inputs:
+        return dx, dxa, dW, xr, xar
+    return dx, dxa, dW
+
+
+def net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, ckpt_every=0, residual=False):
+    """All stages in one kernel.  W: [L, 2E].  Returns (y, ya, ckpt or None)."""
+    lib = _lib.load()
+    _check_inputs(x, xa)
+    x, xa = x.contiguous(), xa.contiguous()
+    B, N, E = x.shape
+    L = W.shape[0]
+    W = _weights(W, L * 2 * E, x.device)
+    y, ya = torch.empty_like(x), torch.empty_like(xa)
+    ckpt = None
+    with torch.cuda.device(x.device):
+        nbytes = lib.ncn_ckpt_bytes(B, N, E, L, ckpt_every)
+        if nbytes:
+            ckpt = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device)
+        rc = lib.ncn_net_fwd(
+            x.data_ptr(), xa.data_ptr(), W.data_ptr(), y.data_ptr(), ya.data_ptr(),
+            ckpt.data_ptr() if ckpt is not None else None, ckpt_every, B, N, E, n_cache, n_head, first_module, L,
+            float(alpha), activation_code(activation), _dtype_code(x), NCN_RESIDUAL if residual else 0, _stream(),
+        )
+    _lib.check("ncn_net_fwd", rc)
+    return y, ya, ckpt
+
+
+def net_bwd(s0, s1, dy, dya, W, alpha, activation, n_cache, n_head, first_module=0, ckpt=None, ckpt_every=0,
+            recompute=False, residual=False, want_inputs=False, dW_out: Optional[torch.Tensor] = None):
+    """Backward of net_fwd in one kernel.  (s0, s1) = net output, or net input with recompute.
+    Returns (dx, dxa, dW[L, 2E]) (+ rebuilt x, xa with want_inputs).  With dW_out the gradient is
+    accumulated into that tensor."""
+    lib = _lib.load()
+    _check_inputs(s0, s1, dy, dya)
+    s0, s1, dy, dya = s0.contiguous(), s1.contiguous(), dy.contiguous(), dya.contiguous()
+    B, N, E = s0.shape
+    L = W.shape[0]
+    W = _weights(W, L * 2 * E, s0.device)
+    dx, dxa = torch.empty_like(s0), torch.empty_like(s0)
+    xr = torch.empty_like(s0) if want_inputs else None
+    xar = torch.empty_like(s0) if want_inputs else None
+    accumulate = dW_out is not None
+    dW = dW_out if accumulate else torch.empty(L, 2 * E, dtype=torch.float32, device=s0.device)
+    flags = (NCN_RECOMPUTE if recompute else 0) | (NCN_RESIDUAL if residual else 0)
+    dt = _dtype_code(s0)
+    with torch.cuda.device(s0.device):
+        ws = _workspace(lib, s0.device, B, N, E, n_cache, n_head, L, dt)
+        rc = lib.ncn_net_bwd(
+            s0.data_ptr(), s1.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(), dxa.data_ptr(),
+            xr.data_ptr() if want_inputs else None, xar.data_ptr() if want_inputs else None, dW.data_ptr(),
+            ckpt.data_ptr() if ckpt is not None else None, ckpt_every, ws.data_ptr(), ws.numel(), B, N, E, n_cache,
+            n_head, first_module, L, float(alpha), activation_code(activation), dt, flags, int(accumulate), _stream(),
+        )
+    _lib.check("ncn_net_bwd", rc)
+    if want_inputs:
+        return dx, dxa, dW, xr, xar
+    return dx, dxa, dW
+
+
+def device_status() -> None:
+    """Raises if a kernel abandoned a bounded wait since the last check (synchronises)."""
+    lib = _lib.load()
+    _lib.check("ncn_device_status", lib.ncn_device_status())

@@ -1,0 +1,286 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle and the golden vectors.
+
+Tolerances: fp32 1e-5 and bf16 2e-2, as max|a-b| / max|b| per tensor (oracle.rel_err).
+"""
+import pytest
+import torch
+
+from oracle import ncn_oracle as O
+from tests.golden_util import golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+TOL32 = 1e-5
+TOLBF = 2e-2
+
+
+@pytest.fixture(scope="module")
+def ncn():
+    import ncn_cuda_b200
+
+    return ncn_cuda_b200
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def run_net(ncn, cls_name, g_or_inputs, activation, n, C, backward_mode=None, dtype=torch.float32):
+    x, xa, ws, dy, dya = g_or_inputs
+    xd = dev(x).to(dtype).requires_grad_(True)
+    xad = dev(xa).to(dtype).requires_grad_(True)
+    wd = [dev(w).clone().requires_grad_(True) for w in ws]
+    cls = getattr(ncn, cls_name)
+    if cls_name == "NCNNetTestCuda":
+        kw = {} if backward_mode is None else {"backward_mode": backward_mode}
+        net = cls(0.9, activation, n, C, len(ws), wd, **kw)
+    else:
+        net = cls(0.9, activation, len(ws), n, C, wd)
+    y, ya = net(xd, xad)
+    torch.autograd.backward([y, ya], [dev(dy).to(dtype), dev(dya).to(dtype)])
+    ncn.ops.device_status()
+    return y.detach(), ya.detach(), xd.grad, xad.grad, [w.grad for w in wd]
+
+
+def assert_close(got, want, tol):
+    y, ya, dx, dxa, dWs = got
+    ry, rya, rdx, rdxa, rdWs = want
+    assert O.rel_err(y.float(), ry) < tol, ("y", O.rel_err(y.float(), ry))
+    assert O.rel_err(ya.float(), rya) < tol, ("ya", O.rel_err(ya.float(), rya))
+    assert O.rel_err(dx.float(), rdx) < tol, ("dx", O.rel_err(dx.float(), rdx))
+    assert O.rel_err(dxa.float(), rdxa) < tol, ("dxa", O.rel_err(dxa.float(), rdxa))
+    for l, (a, b) in enumerate(zip(dWs, rdWs)):
+        assert O.rel_err(a, b) < tol, (f"dW{l}", O.rel_err(a, b))
+
+
+# ---------------------------------------------------------------- golden vectors (reference outputs)
+@pytest.mark.parametrize("name", golden_names())
+def test_golden(ncn, name):
+    g = load_golden(name)
+    inputs = (g["x"], g["xa"], g["W"], g["dy"], g["dya"])
+    got = run_net(ncn, "NCNNetTestCuda", inputs, g["activation"], g["n"], g["C"])
+    want = (g["y"], g["ya"], g["dx"], g["dxa"], g["dW"])
+    # the 32-step reversible chain of the reference's own bench shape grows fp32 rounding ~30x
+    tol = 5e-5 if "refbench" in name else TOL32
+    assert_close(got, want, tol)
+
+
+@pytest.mark.parametrize("name", ["e1_n2_L6", "cfg2_d4096_n4_L6", "cfg4_d4096_n8_L4", "e1_n4_L3_linear"])
+def test_golden_invertible_surface(ncn, name):
+    """RefInvTorchNaive surface = pure reversible backward from the net output."""
+    g = load_golden(name)
+    inputs = (g["x"], g["xa"], g["W"], g["dy"], g["dya"])
+    got = run_net(ncn, "RefInvTorchNaive", inputs, g["activation"], g["n"], g["C"])
+    want = (g["y"], g["ya"], g["dx"], g["dxa"], g["dW"])
+    # 24-32 inverse steps: a few 1e-6 on dx, up to ~1e-5 on a two-element dW of one row
+    assert_close(got, want, 3e-5)
+
+
+def test_golden_reftorchnaive_surface(ncn):
+    g = load_golden("cfg1_d1024_n2_L10")
+    inputs = (g["x"], g["xa"], g["W"], g["dy"], g["dya"])
+    got = run_net(ncn, "RefTorchNaive", inputs, "tanh", g["n"], g["C"])
+    assert_close(got, (g["y"], g["ya"], g["dx"], g["dxa"], g["dW"]), TOL32)
+
+
+# ---------------------------------------------------------------- per-stage operator vs oracle
+STAGE_CASES = [
+    # B, N, E, C, n, module_l, activation
+    (3, 64, 1, 1, 2, 0, "tanh"),
+    (3, 64, 1, 1, 4, 3, "tanh"),
+    (2, 96, 1, 1, 8, 2, "linear"),     # m = 12
+    (2, 128, 1, 1, 16, 4, "sigmoid"),
+    (2, 36, 1, 1, 3, 2, "tanh"),       # n = 3: generic kernel, m = 12
+    (2, 64, 1, 1, 32, 1, "tanh"),      # n = 32: generic kernel
+    (2, 48, 8, 2, 4, 2, "tanh"),
+    (2, 40, 6, 3, 5, 1, "relu"),
+    (1, 64, 128, 4, 32, 1, "tanh"),
+    (2, 32, 40, 1, 8, 3, "linear"),    # d = 40 > 32
+    (5, 30, 1, 1, 2, 3, "tanh"),       # N % 4 != 0: generic kernel
+]
+
+
+@pytest.mark.parametrize("B,N,E,C,n,l,act", STAGE_CASES)
+def test_stage_fwd_bwd(ncn, B, N, E, C, n, l, act):
+    torch.manual_seed(B * 1000 + N + E)
+    x, xa = torch.randn(B, N, E), torch.randn(B, N, E) * 0.3
+    W = torch.randn(2 * E) * (0.5 / E ** 0.5)
+    dy, dya = torch.randn(B, N, E), torch.randn(B, N, E)
+    code = ncn.ops.ACTIVATION_CODES[act]
+    xd, xad, Wd = dev(x).requires_grad_(), dev(xa).requires_grad_(), dev(W).requires_grad_()
+    y, ya = ncn.fused_ncn_cuda_v2(xd, xad, Wd, 0.9, code, n, C, l)
+    torch.autograd.backward([y, ya], [dev(dy), dev(dya)])
+    xr = x.clone().requires_grad_(); xar = xa.clone().requires_grad_(); Wr = W.clone().requires_grad_()
+    ry, rya = O.stage_forward(xr, xar, Wr, 0.9, act, n, C, l)
+    torch.autograd.backward([ry, rya], [dy, dya])
+    tol = 3e-5 if n >= 32 else TOL32
+    assert_close((y.detach(), ya.detach(), xd.grad, xad.grad, [Wd.grad]), (ry.detach(), rya.detach(), xr.grad, xar.grad, [Wr.grad]), tol)
+    # the rebuilt stage input
+    out = ncn.ops.stage_bwd(y.detach(), ya.detach(), dev(dy), dev(dya), Wd.detach(), 0.9, code, n, C, l, want_inputs=True)
+    assert O.rel_err(out[3], x) < tol and O.rel_err(out[4], xa) < 10 * tol
+
+
+def test_stage_bf16(ncn):
+    B, N, E, C, n, l = 4, 256, 1, 1, 8, 2
+    torch.manual_seed(5)
+    x = torch.randn(B, N, E).bfloat16(); xa = (torch.randn(B, N, E) * 0.3).bfloat16()
+    W = torch.randn(2 * E) * 0.3
+    y, ya = ncn.ops.stage_fwd(dev(x), dev(xa), dev(W), 0.9, 0, n, C, l)
+    ry, rya = O.stage_forward(x.float(), xa.float(), W, 0.9, "tanh", n, C, l)
+    assert O.rel_err(y.float(), ry) < TOLBF and O.rel_err(ya.float(), rya) < TOLBF
+    # multi-feature bf16 through the generic kernel
+    x = torch.randn(2, 64, 16).bfloat16(); xa = torch.zeros(2, 64, 16).bfloat16(); W = torch.randn(32) * 0.2
+    y, ya = ncn.ops.stage_fwd(dev(x), dev(xa), dev(W), 0.9, 0, 8, 2, 1)
+    ry, rya = O.stage_forward(x.float(), xa.float(), W, 0.9, "tanh", 8, 2, 1)
+    assert O.rel_err(y.float(), ry) < TOLBF and O.rel_err(ya.float(), rya) < TOLBF
+
+
+# ---------------------------------------------------------------- fused nets vs oracle, all modes
+NET_CASES = [
+    # B, N, n, L, w_var, activation
+    (64, 1024, 2, 10, 0.5, "tanh"),
+    (32, 4096, 4, 6, 0.25, "tanh"),
+    (16, 4096, 8, 4, 0.01, "tanh"),
+    (8, 8192, 16, 4, 1 / 16, "tanh"),
+    (48, 2048, 8, 4, 1 / 8, "tanh"),
+    (100, 96, 4, 7, 0.25, "linear"),  # m = 24, ragged last tile, stride wrap
+    (7, 40, 2, 5, 0.3, "relu"),       # m = 20
+    (5, 64, 4, 1, 0.3, "sigmoid"),    # single stage through the net call
+]
+
+
+@pytest.mark.parametrize("B,N,n,L,var,act", NET_CASES)
+@pytest.mark.parametrize("mode", ["checkpoint", "recompute", "invert"])
+def test_net_modes(ncn, B, N, n, L, var, act, mode):
+    inputs = O.make_inputs(7, B, N, 1, L, var, dya_zero=False)
+    x, xa, ws, dy, dya = inputs
+    want = O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, act, n, 1)
+    got = run_net(ncn, "NCNNetTestCuda", inputs, act, n, 1, backward_mode=mode)
+    steps = n * L
+    if mode == "invert":  # rounding grows 1/0.9 per rebuilt step
+        tol = TOL32 if steps <= 16 else (5e-5 if steps <= 40 else 1e-2)
+    elif mode == "recompute":
+        tol = TOL32 if steps <= 16 else (5e-5 if steps <= 40 else 1e-2)
+    else:
+        tol = TOL32
+    assert_close(got, want, tol)
+
+
+def test_fused_equals_stagewise_forward(ncn):
+    x, xa, ws, _, _ = O.make_inputs(3, 16, 512, 1, 5, 0.25)
+    xd, xad = dev(x), dev(xa)
+    W = torch.stack([dev(w) for w in ws])
+    y, ya, _ = ncn.ops.net_fwd(xd, xad, W, 0.9, 0, 4, 1)
+    for l in range(5):
+        xd, xad = ncn.ops.stage_fwd(xd, xad, W[l], 0.9, 0, 4, 1, l)
+    assert torch.equal(y, xd) and torch.equal(ya, xad)
+
+
+def test_first_module_offset(ncn):
+    x, xa, ws, _, _ = O.make_inputs(4, 8, 256, 1, 3, 0.25)
+    W = torch.stack([dev(w) for w in ws])
+    y, ya, _ = ncn.ops.net_fwd(dev(x), dev(xa), W, 0.9, 0, 4, 1, first_module=2)
+    ry, rya = O.net_forward(x, xa, ws, 0.9, "tanh", 4, 1, first_module=2)
+    assert O.rel_err(y, ry) < TOL32 and O.rel_err(ya, rya) < TOL32
+
+
+def test_dw_bitwise_reproducible(ncn):
+    inputs = O.make_inputs(9, 512, 1024, 1, 4, 0.25, dya_zero=False)
+    a = run_net(ncn, "NCNNetTestCuda", inputs, "tanh", 4, 1)
+    b = run_net(ncn, "NCNNetTestCuda", inputs, "tanh", 4, 1)
+    for u, v in zip(a[4], b[4]):
+        assert torch.equal(u, v)
+    assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+
+
+# ---------------------------------------------------------------- bf16 storage, fp32 math
+@pytest.mark.parametrize("B,N,n,L,var", [(16, 8192, 16, 4, 1 / 16), (32, 2048, 8, 4, 1 / 8)])
+def test_net_bf16(ncn, B, N, n, L, var):
+    x, xa, ws, dy, dya = O.make_inputs(2, B, N, 1, L, var, dya_zero=False)
+    x, dy, dya = x.bfloat16().float(), dy.bfloat16().float(), dya.bfloat16().float()
+    want = O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, "tanh", n, 1)
+    got = run_net(ncn, "NCNNetTestCuda", (x, xa, ws, dy, dya), "tanh", n, 1, dtype=torch.bfloat16)
+    assert_close(got, want, TOLBF)
+
+
+# ---------------------------------------------------------------- residual stack
+def test_residual_stack(ncn):
+    layers, L, n, N, B = 3, 4, 8, 512, 24
+    torch.manual_seed(4)
+    x = torch.randn(B, N, 1); xa = torch.zeros(B, N, 1)
+    W = torch.randn(layers, L, 2) * (1 / 8) ** 0.5
+    dy, dya = torch.randn(B, N, 1), torch.randn(B, N, 1)
+    lws = [[W[k, l] for l in range(L)] for k in range(layers)]
+    ry, rya, rdx, rdxa, rdW = O.stack_fwd_bwd(x, xa, lws, dy, dya, 0.9, "tanh", n, 1)
+    stack = ncn.NCNResidualStack(layers, 0.9, "tanh", n, 1, L, 1).cuda()
+    with torch.no_grad():
+        stack.weight.copy_(dev(W))
+    xd, xad = dev(x).requires_grad_(), dev(xa).requires_grad_()
+    y, ya = stack(xd, xad)
+    torch.autograd.backward([y, ya], [dev(dy), dev(dya)])
+    assert O.rel_err(y, ry) < TOL32 and O.rel_err(ya, rya) < TOL32
+    assert O.rel_err(xd.grad, rdx) < 5e-5 and O.rel_err(xad.grad, rdxa) < 5e-5
+    for k in range(layers):
+        for l in range(L):
+            assert O.rel_err(stack.weight.grad[k, l], rdW[k][l]) < 5e-5
+
+
+# ---------------------------------------------------------------- modules keep the reference surface
+def test_module_surface_and_state_dict(ncn):
+    net = ncn.NCNNetCuda(0.9, "tanh", 4, 1, 3, 1).cuda()
+    sd = net.state_dict()
+    assert sorted(sd) == [f"ncn_modules.{l}.weight" for l in range(3)]
+    assert all(v.shape == (2,) for v in sd.values())
+    x = torch.randn(4, 64, 1, device="cuda", requires_grad=True)
+    xa = torch.zeros(4, 64, 1, device="cuda", requires_grad=True)
+    y, ya = net(x, xa)
+    (y.sum() + ya.sum()).backward()
+    assert all(m.weight.grad is not None for m in net.ncn_modules)
+    ws = [m.weight.detach().cpu() for m in net.ncn_modules]
+    ry, _ = O.net_forward(x.detach().cpu(), xa.detach().cpu(), ws, 0.9, "tanh", 4, 1)
+    assert O.rel_err(y, ry) < TOL32
+    # multi-feature net: stage-by-stage path, same surface
+    net2 = ncn.NCNNetCuda(0.9, "tanh", 8, 2, 2, 16).cuda()
+    x2 = torch.randn(2, 64, 16, device="cuda", requires_grad=True)
+    y2, ya2 = net2(x2, torch.zeros_like(x2))
+    y2.sum().backward()
+    ws2 = [m.weight.detach().cpu() for m in net2.ncn_modules]
+    ry2, _ = O.net_forward(x2.detach().cpu(), torch.zeros(2, 64, 16), ws2, 0.9, "tanh", 8, 2)
+    assert O.rel_err(y2, ry2) < TOL32
+
+
+def test_group_function_surface(ncn):
+    n, d = 8, 16
+    torch.manual_seed(1)
+    xi, xa = torch.randn(n, d), torch.randn(n, d) * 0.2
+    Wi, Wj = torch.randn(d) * 0.2, torch.randn(d) * 0.2
+    a = [dev(t).requires_grad_() for t in (xi, xa, Wi, Wj)]
+    yi, ya = ncn.NCNFunctionPytorch.apply(a[0], a[1], a[2], a[3], 0.9, "tanh", 1, n, 0)
+    (yi.sum() + 2 * ya.sum()).backward()
+    r = [t.clone().requires_grad_() for t in (xi, xa, Wi, Wj)]
+    ry, rya = O.stage_forward(r[0][None], r[1][None], torch.cat([r[2], r[3]]), 0.9, "tanh", n, 1, 0)
+    (ry.sum() + 2 * rya.sum()).backward()
+    assert O.rel_err(yi, ry[0]) < TOL32
+    for u, v in zip(a, r):
+        assert O.rel_err(u.grad, v.grad) < TOL32
+
+
+# ---------------------------------------------------------------- errors
+def test_error_behaviour(ncn):
+    from ncn_cuda_b200._lib import NCNError
+
+    x = torch.randn(2, 30, 4, device="cuda")
+    W = torch.randn(8, device="cuda")
+    with pytest.raises(NCNError) as e:
+        ncn.ops.stage_fwd(x, x, W, 0.9, 0, 4, 1, 0)       # 4 does not divide 30
+    assert e.value.status == 1
+    with pytest.raises(NCNError):
+        ncn.ops.stage_fwd(x, x, W, 0.9, 0, 5, 3, 0)       # 3 heads do not divide E = 4
+    with pytest.raises(TypeError):
+        ncn.ops.stage_fwd(x.double(), x.double(), W, 0.9, 0, 5, 1, 0)
+    with pytest.raises(RuntimeError):
+        ncn.ops.stage_fwd(x.cpu(), x.cpu(), W, 0.9, 0, 5, 1, 0)
+    with pytest.raises(NCNError) as e:
+        ncn.ops.net_fwd(x, x, W.reshape(1, 8), 0.9, 0, 5, 1)  # E != 1: fused path does not apply
+    assert e.value.status == 5
+    ncn.ops.device_status()
