@@ -119,7 +119,7 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
     p.off_out = take(out_b);
     p.off_ckpt = slots ? take(ck_b) : kNoOff;
     p.off_red = take(bwd ? (uint64_t)2 * L * nwarp * 4 : 0);
-    p.off_w = take((uint64_t)2 * L * 4);
+    p.off_w = take((uint64_t)16 * L);  // one StageRec per stage
     p.off_bar = take(32);
     if (off > limit) return false;
     p.threads = threads;

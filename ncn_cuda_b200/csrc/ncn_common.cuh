@@ -232,86 +232,207 @@ __host__ __device__ __forceinline__ int stage_stride(int stage, int m) {
 }
 
 // ------------------------------------------------------------------ step math (one feature per position)
-// One group of NG positions, all NG steps.  T_i = alpha x_i + (1-alpha)(x_i wi + xj wj) xj is
-// evaluated as x_i * p + q with p = alpha + (1-alpha) wi xj, q = (1-alpha) wj xj^2.
-template <int NG, int ACT>
-__device__ __forceinline__ void group_forward(float (&x)[NG], float (&a)[NG], float wi_s, float wj_s, float alpha) {
-  // wi_s = (1-alpha) wi, wj_s = (1-alpha) wj
+//
+// One step of the reference (torch_ref/ncn_pytorch.py:74-94), per position i of a group:
+//     T_i = alpha x_i + (1-alpha)(x_i wi + xj wj) xj ;  F = act(T)
+//     a_i <- m a_i + c F ;  x_i <- m x_i + c a_i                     (m = 0.9, c = 0.1)
+// Every position takes exactly one such step per j, so the factors of m can be carried as a
+// scale that is uniform over the group: with k steps done, x = m^k (X + D_k), a = m^k (A + C_k),
+// where X, A are the per-position registers and C_k, D_k compile-time constants (non-zero only
+// when the activation has a constant part, F = f0 + f1 r).  In these variables a step is
+//     X-part of T:  Ts = X P + Q   (P, Q formed once per step from xj)
+//     A <- A + (c f1 / m^(k+1)) r ;  X <- X + c A
+// i.e. four FMA-pipe instructions and the activation's special-function instructions per
+// position and step.  After the NG steps of a stage the true values are restored.
+constexpr double kMd = 0.89999997615814208984375;    // (double)0.9f
+constexpr double kCd = 0.100000001490116119384765625;  // (double)0.1f
+
+constexpr double cpow(double b, int e) {
+  double r = 1.0;
+  for (int i = 0; i < e; ++i) r *= b;
+  return r;
+}
+
+// Activation written as F = f0 + f1 * r(Ts), Ts = sT * T, and act'(T) = ds * u(Ts, r).
+template <int ACT>
+struct ActForm;
+template <>
+struct ActForm<ACT_TANH> {  // tanh T = 1 - 2 / (2^(2 log2e T) + 1) ; 1 - F^2 = 4 (r - r^2)
+  static constexpr double sT = 2.8853900817779268, f0 = 1.0, f1 = -2.0, ds = 4.0;
+  static __device__ __forceinline__ float r(float ts) { return rcp_approx(ex2_approx(ts) + 1.0f); }
+  static __device__ __forceinline__ float gt(float g, float, float r) { return g * fmaf(-r, r, r); }
+};
+template <>
+struct ActForm<ACT_SIGMOID> {  // 1 / (1 + 2^(-log2e T)) ; F' = F (1 - F)
+  static constexpr double sT = -1.4426950408889634, f0 = 0.0, f1 = 1.0, ds = 1.0;
+  static __device__ __forceinline__ float r(float ts) { return rcp_approx(ex2_approx(ts) + 1.0f); }
+  static __device__ __forceinline__ float gt(float g, float, float r) { return g * fmaf(-r, r, r); }
+};
+template <>
+struct ActForm<ACT_RELU> {
+  static constexpr double sT = 1.0, f0 = 0.0, f1 = 1.0, ds = 1.0;
+  static __device__ __forceinline__ float r(float ts) { return fmaxf(ts, 0.0f); }
+  static __device__ __forceinline__ float gt(float g, float ts, float) { return ts > 0.0f ? g : 0.0f; }
+};
+template <>
+struct ActForm<ACT_LINEAR> {
+  static constexpr double sT = 1.0, f0 = 0.0, f1 = 1.0, ds = 1.0;
+  static __device__ __forceinline__ float r(float ts) { return ts; }
+  static __device__ __forceinline__ float gt(float g, float, float) { return g; }
+};
+
+// forward offsets after k steps: C_k = sum_{i=1..k} c f0 / m^i ; D_k = sum_{i=1..k} c C_i
+constexpr double fwd_C(int k, double f0) {
+  double C = 0.0;
+  for (int i = 1; i <= k; ++i) C += kCd * f0 / cpow(kMd, i);
+  return C;
+}
+constexpr double fwd_D(int k, double f0) {
+  double C = 0.0, D = 0.0;
+  for (int i = 1; i <= k; ++i) {
+    C += kCd * f0 / cpow(kMd, i);
+    D += kCd * C;
+  }
+  return D;
+}
+// reverse offsets after k inverse steps: x = m^-k (X + DX_k), a = m^-k (A + CA_k)
+//   CA_{k+1} = CA_k - c f0 m^k ;  DX_{k+1} = DX_k - c CA_k
+constexpr double bwd_CA(int k, double f0) {
+  double CA = 0.0;
+  for (int i = 0; i < k; ++i) CA -= kCd * f0 * cpow(kMd, i);
+  return CA;
+}
+constexpr double bwd_DX(int k, double f0) {
+  double CA = 0.0, DX = 0.0;
+  for (int i = 0; i < k; ++i) {
+    DX -= kCd * CA;
+    CA -= kCd * f0 * cpow(kMd, i);
+  }
+  return DX;
+}
+
+// weights of one stage as the step code wants them
+struct StageW {
+  float owi, owj;  // (1-alpha) wi, (1-alpha) wj
+  float alpha, oma;
+};
+
+template <int NG, int ACT, int J>
+struct FwdSteps {
+  static __device__ __forceinline__ void run(float (&X)[NG], float (&A)[NG], float owi_s, float owj_s, float alpha_s) {
+    using F = ActForm<ACT>;
+    constexpr float mk = (float)cpow(kMd, J);
+    constexpr float mkDk = (float)(cpow(kMd, J) * fwd_D(J, F::f0));
+    constexpr float cA = (float)(kCd * F::f1 / cpow(kMd, J + 1));
+    const float xj = fmaf(X[J], mk, mkDk);
+    const float pp = fmaf(owi_s, xj, alpha_s);  // sT (alpha + (1-alpha) wi xj)
+    const float P = pp * mk;
+    const float Q = fmaf(pp, mkDk, (owj_s * xj) * xj);
 #pragma unroll
-  for (int j = 0; j < NG; ++j) {
-    const float xj = x[j];
-    if constexpr (ACT == ACT_TANH) {
-      constexpr float k2 = 2.8853900817779268f;  // 2 log2(e)
-      const float p = fmaf(wi_s, xj, alpha) * k2;
-      const float q = (wj_s * xj) * xj * k2;
-#pragma unroll
-      for (int i = 0; i < NG; ++i) {
-        const float e = ex2_approx(fmaf(x[i], p, q));
-        const float r = rcp_approx(e + 1.0f);
-        // a' = m a + c (1 - 2r)
-        a[i] = fmaf(r, -2.0f * kC, fmaf(a[i], kM, kC));
-        x[i] = fmaf(a[i], kC, x[i] * kM);
-      }
-    } else {
-      const float p = fmaf(wi_s, xj, alpha);
-      const float q = (wj_s * xj) * xj;
-#pragma unroll
-      for (int i = 0; i < NG; ++i) {
-        const float f = act_fwd<ACT>(fmaf(x[i], p, q));
-        a[i] = fmaf(f, kC, a[i] * kM);
-        x[i] = fmaf(a[i], kC, x[i] * kM);
-      }
+    for (int i = 0; i < NG; ++i) {
+      const float r = F::r(fmaf(X[i], P, Q));
+      A[i] = fmaf(r, cA, A[i]);
+      X[i] = fmaf(A[i], kC, X[i]);
     }
+    FwdSteps<NG, ACT, J + 1>::run(X, A, owi_s, owj_s, alpha_s);
+  }
+};
+template <int NG, int ACT>
+struct FwdSteps<NG, ACT, NG> {
+  static __device__ __forceinline__ void run(float (&)[NG], float (&)[NG], float, float, float) {}
+};
+
+// All NG steps of one group; x, a hold true values on entry and on exit.
+template <int NG, int ACT>
+__device__ __forceinline__ void group_forward(float (&x)[NG], float (&a)[NG], const StageW& w) {
+  using F = ActForm<ACT>;
+  constexpr float sT = (float)F::sT;
+  FwdSteps<NG, ACT, 0>::run(x, a, w.owi * sT, w.owj * sT, w.alpha * sT);
+  constexpr float mN = (float)cpow(kMd, NG);
+  constexpr float mNC = (float)(cpow(kMd, NG) * fwd_C(NG, F::f0));
+  constexpr float mND = (float)(cpow(kMd, NG) * fwd_D(NG, F::f0));
+#pragma unroll
+  for (int i = 0; i < NG; ++i) {
+    x[i] = fmaf(x[i], mN, mND);
+    a[i] = fmaf(a[i], mN, mNC);
   }
 }
 
-// Reverse sweep of one group: on entry (x, a) hold the group's OUTPUT and (gx, ga) the incoming
-// cotangents; on exit they hold the group's input and the outgoing cotangents.  dwi/dwj are
-// incremented by the group's weight-gradient contribution.
-// Per step (torch_ref/ncn_pytorch_invertible.py:97-111 inverse, :164-172 gradient):
-//   x = (y - c ya)/m ; F = act(T(x)) ; a = (ya - c F)/m
-//   gA' = ga + c gy ; gT = c gA' act'(T) ; ga <- m gA'
-//   gx_i = m gy_i + gT_i p ;  gx_j += (1-alpha) sum_i gT_i (x_i wi + 2 wj xj)
-//   dWi += (1-alpha) xj sum_i gT_i x_i ;  dWj += (1-alpha) xj^2 sum_i gT_i
-template <int NG, int ACT>
-__device__ __forceinline__ void group_backward(float (&x)[NG], float (&a)[NG], float (&gx)[NG], float (&ga)[NG],
-                                               float wi, float wj, float alpha, float oma, float& dwi, float& dwj) {
+// Reverse sweep (torch_ref/ncn_pytorch_invertible.py:97-111 inverse, :164-172 gradient).  With k
+// inverse steps done: x = m^-k (X + DX_k), a = m^-k (A + CA_k), gy = m^k H, ga = m^k G.  Per step:
+//   X <- X - c A                              (x_prev = (y - c ya)/m)
+//   r from Ts = X Ps + Qs ;  A <- A - c f1 m^k r  (a_prev = (ya - c F)/m)
+//   G <- G + c H            (gA' = ga + c gy ; ga_prev = m gA')
+//   gt = G u                (gT = c ds m^k gt)
+//   H <- H + gt (c ds p / m)                  (gx_i = m gy_i + gT_i p)
+//   aI += gt X ; aS += gt                     (sums for gx_j, dWi, dWj)
+template <int NG, int ACT, int J>
+struct BwdSteps {
+  static __device__ __forceinline__ void run(float (&X)[NG], float (&A)[NG], float (&H)[NG], float (&G)[NG],
+                                             const StageW& w, float& dwi, float& dwj) {
+    using F = ActForm<ACT>;
+    constexpr int k = NG - 1 - J;
+    constexpr double mkd = cpow(kMd, k);
+    constexpr float imk1 = (float)(1.0 / cpow(kMd, k + 1));
+    constexpr float DX1 = (float)bwd_DX(k + 1, F::f0);
+    constexpr float imk1DX1 = (float)(bwd_DX(k + 1, F::f0) / cpow(kMd, k + 1));
+    constexpr float cAr = (float)(-kCd * F::f1 * mkd);
+    constexpr float sTimk1 = (float)(F::sT / cpow(kMd, k + 1));
+    constexpr float sT = (float)F::sT;
+    constexpr float cdsm = (float)(kCd * F::ds / kMd);
+    constexpr float cdsmk = (float)(kCd * F::ds * mkd);
 #pragma unroll
-  for (int j = NG - 1; j >= 0; --j) {
-#pragma unroll
-    for (int i = 0; i < NG; ++i) x[i] = fmaf(a[i], -kCoverM, x[i] * kInvM);
-    const float xj = x[j];
-    const float p = fmaf(oma * wi, xj, alpha);
-    const float q = (oma * wj * xj) * xj;
-    float accI = 0.0f, accS = 0.0f;
+    for (int i = 0; i < NG; ++i) X[i] = fmaf(-kC, A[i], X[i]);
+    const float xj = fmaf(X[J], imk1, imk1DX1);
+    const float pp = fmaf(w.owi, xj, w.alpha);  // p = alpha + (1-alpha) wi xj
+    const float Ps = pp * sTimk1;
+    const float Qs = fmaf(Ps, DX1, (w.owj * sT * xj) * xj);
+    const float PH = pp * cdsm;
+    float aI = 0.0f, aS = 0.0f;
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
-      float dact;
-      if constexpr (ACT == ACT_TANH) {
-        constexpr float k2 = 2.8853900817779268f;
-        const float e = ex2_approx(fmaf(x[i], p * k2, q * k2));
-        const float r = rcp_approx(e + 1.0f);
-        // a = (ya - c (1 - 2r)) / m ; act' = 1 - F^2 = 4 (r - r^2)
-        a[i] = fmaf(r, 2.0f * kCoverM, fmaf(a[i], kInvM, -kCoverM));
-        dact = 4.0f * fmaf(-r, r, r);
-      } else {
-        const float t = fmaf(x[i], p, q);
-        const float f = act_fwd<ACT>(t);
-        a[i] = fmaf(f, -kCoverM, a[i] * kInvM);
-        dact = act_grad<ACT>(t, f);
-      }
-      const float gAp = fmaf(kC, gx[i], ga[i]);
-      const float gT = (kC * gAp) * dact;
-      ga[i] = kM * gAp;
-      gx[i] = fmaf(gT, p, kM * gx[i]);
-      accI = fmaf(gT, x[i], accI);
-      accS += gT;
+      const float ts = fmaf(X[i], Ps, Qs);
+      const float r = F::r(ts);
+      A[i] = fmaf(r, cAr, A[i]);
+      G[i] = fmaf(kC, H[i], G[i]);
+      const float gt = F::gt(G[i], ts, r);
+      H[i] = fmaf(gt, PH, H[i]);
+      aI = fmaf(gt, X[i], aI);
+      aS += gt;
     }
-    // sum_i gT_i (x_i wi + 2 wj xj) = wi accI + 2 wj xj accS
-    const float oxj = oma * xj;
-    gx[j] = fmaf(oma, fmaf(wi, accI, 2.0f * wj * xj * accS), gx[j]);
-    dwi = fmaf(oxj, accI, dwi);
-    dwj = fmaf(oxj * xj, accS, dwj);
+    const float tI = fmaf(DX1, aS, aI) * cdsm;  // sum_i gT_i x_i
+    const float tS = aS * cdsmk;                // sum_i gT_i
+    // gx_j += (1-alpha) (wi sum gT x + 2 wj xj sum gT), in units of m^(k+1)
+    H[J] = fmaf(fmaf(w.owi, tI, 2.0f * w.owj * xj * tS), imk1, H[J]);
+    const float oxj = w.oma * xj;
+    dwi = fmaf(oxj, tI, dwi);
+    dwj = fmaf(oxj * xj, tS, dwj);
+    BwdSteps<NG, ACT, J - 1>::run(X, A, H, G, w, dwi, dwj);
+  }
+};
+template <int NG, int ACT>
+struct BwdSteps<NG, ACT, -1> {
+  static __device__ __forceinline__ void run(float (&)[NG], float (&)[NG], float (&)[NG], float (&)[NG], const StageW&,
+                                             float&, float&) {}
+};
+
+// On entry (x, a) hold the group's OUTPUT and (gx, ga) the incoming cotangents; on exit the
+// group's input and the outgoing cotangents.  dwi/dwj gain the group's weight gradient.
+template <int NG, int ACT>
+__device__ __forceinline__ void group_backward(float (&x)[NG], float (&a)[NG], float (&gx)[NG], float (&ga)[NG],
+                                               const StageW& w, float& dwi, float& dwj) {
+  using F = ActForm<ACT>;
+  BwdSteps<NG, ACT, NG - 1>::run(x, a, gx, ga, w, dwi, dwj);
+  constexpr float imN = (float)(1.0 / cpow(kMd, NG));
+  constexpr float imNDX = (float)(bwd_DX(NG, F::f0) / cpow(kMd, NG));
+  constexpr float imNCA = (float)(bwd_CA(NG, F::f0) / cpow(kMd, NG));
+  constexpr float mN = (float)cpow(kMd, NG);
+#pragma unroll
+  for (int i = 0; i < NG; ++i) {
+    x[i] = fmaf(x[i], imN, imNDX);
+    a[i] = fmaf(a[i], imN, imNCA);
+    gx[i] *= mN;
+    ga[i] *= mN;
   }
 }
 
