@@ -2,6 +2,7 @@
 // Declarations and the reference interfaces they replace are in include/ncn_b200.h.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/ncn_b200.h"
@@ -95,7 +96,13 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
                      const DevInfo& dev, int act, Plan& pl) {
   const int w = dtype == DT_BF16 ? 2 : 4;
   const int m = N / n;
-  const int maxT = rows_max_threads(n, bwd);
+  int maxT = rows_max_threads(n, bwd);
+  int force_nbuf = 0;
+  if (const char* e = std::getenv(bwd ? "NCN_BWD_THREADS" : "NCN_FWD_THREADS")) {  // tuning experiments
+    const int t = std::atoi(e);
+    if (t >= 32 && t <= maxT && t % 32 == 0) maxT = t;
+  }
+  if (const char* e = std::getenv("NCN_NBUF")) force_nbuf = std::atoi(e);
   const bool recompute = (flags & F_RECOMPUTE) != 0;
   if (recompute) n_ck = 0;
   int R = m >= maxT ? 1 : maxT / m;
@@ -135,7 +142,7 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
     if (bwd && n_ck > 0) {
       ok = layout(R, 1, n_ck, pl) || layout(R, 1, 0, pl);
     } else {
-      ok = layout(R, 2, 0, pl) || layout(R, 1, 0, pl);
+      ok = (force_nbuf != 1 && layout(R, 2, 0, pl)) || layout(R, 1, 0, pl);
     }
     if (ok) break;
   }

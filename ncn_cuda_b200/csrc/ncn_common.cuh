@@ -253,32 +253,45 @@ constexpr double cpow(double b, int e) {
   return r;
 }
 
+// The per-position arithmetic is issued two positions at a time with the packed fp32
+// instructions of sm_100 (fma.rn.f32x2 / add.f32x2 / mul.f32x2 through __ffma2_rn, __fadd2_rn,
+// __fmul2_rn): the kernels are bound by instruction issue next to the special-function unit, and
+// a packed instruction does the work of two in one issue slot.
+__device__ __forceinline__ float2 f2(float v) { return make_float2(v, v); }
+
 // Activation written as F = f0 + f1 * r(Ts), Ts = sT * T, and act'(T) = ds * u(Ts, r).
 template <int ACT>
 struct ActForm;
 template <>
 struct ActForm<ACT_TANH> {  // tanh T = 1 - 2 / (2^(2 log2e T) + 1) ; 1 - F^2 = 4 (r - r^2)
   static constexpr double sT = 2.8853900817779268, f0 = 1.0, f1 = -2.0, ds = 4.0;
-  static __device__ __forceinline__ float r(float ts) { return rcp_approx(ex2_approx(ts) + 1.0f); }
-  static __device__ __forceinline__ float gt(float g, float, float r) { return g * fmaf(-r, r, r); }
+  static __device__ __forceinline__ float2 r(float2 ts) {
+    const float2 d = __fadd2_rn(make_float2(ex2_approx(ts.x), ex2_approx(ts.y)), f2(1.0f));
+    return make_float2(rcp_approx(d.x), rcp_approx(d.y));
+  }
+  static __device__ __forceinline__ float2 gt(float2 g, float2, float2 r) {
+    return __fmul2_rn(g, __ffma2_rn(make_float2(-r.x, -r.y), r, r));
+  }
 };
 template <>
 struct ActForm<ACT_SIGMOID> {  // 1 / (1 + 2^(-log2e T)) ; F' = F (1 - F)
   static constexpr double sT = -1.4426950408889634, f0 = 0.0, f1 = 1.0, ds = 1.0;
-  static __device__ __forceinline__ float r(float ts) { return rcp_approx(ex2_approx(ts) + 1.0f); }
-  static __device__ __forceinline__ float gt(float g, float, float r) { return g * fmaf(-r, r, r); }
+  static __device__ __forceinline__ float2 r(float2 ts) { return ActForm<ACT_TANH>::r(ts); }
+  static __device__ __forceinline__ float2 gt(float2 g, float2 ts, float2 r) { return ActForm<ACT_TANH>::gt(g, ts, r); }
 };
 template <>
 struct ActForm<ACT_RELU> {
   static constexpr double sT = 1.0, f0 = 0.0, f1 = 1.0, ds = 1.0;
-  static __device__ __forceinline__ float r(float ts) { return fmaxf(ts, 0.0f); }
-  static __device__ __forceinline__ float gt(float g, float ts, float) { return ts > 0.0f ? g : 0.0f; }
+  static __device__ __forceinline__ float2 r(float2 ts) { return make_float2(fmaxf(ts.x, 0.0f), fmaxf(ts.y, 0.0f)); }
+  static __device__ __forceinline__ float2 gt(float2 g, float2 ts, float2) {
+    return make_float2(ts.x > 0.0f ? g.x : 0.0f, ts.y > 0.0f ? g.y : 0.0f);
+  }
 };
 template <>
 struct ActForm<ACT_LINEAR> {
   static constexpr double sT = 1.0, f0 = 0.0, f1 = 1.0, ds = 1.0;
-  static __device__ __forceinline__ float r(float ts) { return ts; }
-  static __device__ __forceinline__ float gt(float g, float, float) { return g; }
+  static __device__ __forceinline__ float2 r(float2 ts) { return ts; }
+  static __device__ __forceinline__ float2 gt(float2 g, float2, float2) { return g; }
 };
 
 // forward offsets after k steps: C_k = sum_{i=1..k} c f0 / m^i ; D_k = sum_{i=1..k} c C_i
@@ -319,42 +332,53 @@ struct StageW {
 
 template <int NG, int ACT, int J>
 struct FwdSteps {
-  static __device__ __forceinline__ void run(float (&X)[NG], float (&A)[NG], float owi_s, float owj_s, float alpha_s) {
+  static __device__ __forceinline__ void run(float2 (&X)[NG / 2], float2 (&A)[NG / 2], float owi_s, float owj_s,
+                                             float alpha_s) {
     using F = ActForm<ACT>;
     constexpr float mk = (float)cpow(kMd, J);
     constexpr float mkDk = (float)(cpow(kMd, J) * fwd_D(J, F::f0));
     constexpr float cA = (float)(kCd * F::f1 / cpow(kMd, J + 1));
-    const float xj = fmaf(X[J], mk, mkDk);
+    const float XJ = (J & 1) ? X[J / 2].y : X[J / 2].x;
+    const float xj = fmaf(XJ, mk, mkDk);
     const float pp = fmaf(owi_s, xj, alpha_s);  // sT (alpha + (1-alpha) wi xj)
-    const float P = pp * mk;
-    const float Q = fmaf(pp, mkDk, (owj_s * xj) * xj);
+    const float2 P = f2(pp * mk);
+    const float2 Q = f2(fmaf(pp, mkDk, (owj_s * xj) * xj));
 #pragma unroll
-    for (int i = 0; i < NG; ++i) {
-      const float r = F::r(fmaf(X[i], P, Q));
-      A[i] = fmaf(r, cA, A[i]);
-      X[i] = fmaf(A[i], kC, X[i]);
+    for (int i = 0; i < NG / 2; ++i) {
+      const float2 r = F::r(__ffma2_rn(X[i], P, Q));
+      A[i] = __ffma2_rn(r, f2(cA), A[i]);
+      X[i] = __ffma2_rn(A[i], f2(kC), X[i]);
     }
     FwdSteps<NG, ACT, J + 1>::run(X, A, owi_s, owj_s, alpha_s);
   }
 };
 template <int NG, int ACT>
 struct FwdSteps<NG, ACT, NG> {
-  static __device__ __forceinline__ void run(float (&)[NG], float (&)[NG], float, float, float) {}
+  static __device__ __forceinline__ void run(float2 (&)[NG / 2], float2 (&)[NG / 2], float, float, float) {}
 };
 
 // All NG steps of one group; x, a hold true values on entry and on exit.
 template <int NG, int ACT>
 __device__ __forceinline__ void group_forward(float (&x)[NG], float (&a)[NG], const StageW& w) {
+  static_assert(NG % 2 == 0, "positions are processed in pairs");
   using F = ActForm<ACT>;
   constexpr float sT = (float)F::sT;
-  FwdSteps<NG, ACT, 0>::run(x, a, w.owi * sT, w.owj * sT, w.alpha * sT);
+  float2 X[NG / 2], A[NG / 2];
+#pragma unroll
+  for (int i = 0; i < NG / 2; ++i) {
+    X[i] = make_float2(x[2 * i], x[2 * i + 1]);
+    A[i] = make_float2(a[2 * i], a[2 * i + 1]);
+  }
+  FwdSteps<NG, ACT, 0>::run(X, A, w.owi * sT, w.owj * sT, w.alpha * sT);
   constexpr float mN = (float)cpow(kMd, NG);
   constexpr float mNC = (float)(cpow(kMd, NG) * fwd_C(NG, F::f0));
   constexpr float mND = (float)(cpow(kMd, NG) * fwd_D(NG, F::f0));
 #pragma unroll
-  for (int i = 0; i < NG; ++i) {
-    x[i] = fmaf(x[i], mN, mND);
-    a[i] = fmaf(a[i], mN, mNC);
+  for (int i = 0; i < NG / 2; ++i) {
+    const float2 xo = __ffma2_rn(X[i], f2(mN), f2(mND));
+    const float2 ao = __ffma2_rn(A[i], f2(mN), f2(mNC));
+    x[2 * i] = xo.x; x[2 * i + 1] = xo.y;
+    a[2 * i] = ao.x; a[2 * i + 1] = ao.y;
   }
 }
 
@@ -368,8 +392,8 @@ __device__ __forceinline__ void group_forward(float (&x)[NG], float (&a)[NG], co
 //   aI += gt X ; aS += gt                     (sums for gx_j, dWi, dWj)
 template <int NG, int ACT, int J>
 struct BwdSteps {
-  static __device__ __forceinline__ void run(float (&X)[NG], float (&A)[NG], float (&H)[NG], float (&G)[NG],
-                                             const StageW& w, float& dwi, float& dwj) {
+  static __device__ __forceinline__ void run(float2 (&X)[NG / 2], float2 (&A)[NG / 2], float2 (&H)[NG / 2],
+                                             float2 (&G)[NG / 2], const StageW& w, float& dwi, float& dwj) {
     using F = ActForm<ACT>;
     constexpr int k = NG - 1 - J;
     constexpr double mkd = cpow(kMd, k);
@@ -382,28 +406,32 @@ struct BwdSteps {
     constexpr float cdsm = (float)(kCd * F::ds / kMd);
     constexpr float cdsmk = (float)(kCd * F::ds * mkd);
 #pragma unroll
-    for (int i = 0; i < NG; ++i) X[i] = fmaf(-kC, A[i], X[i]);
-    const float xj = fmaf(X[J], imk1, imk1DX1);
+    for (int i = 0; i < NG / 2; ++i) X[i] = __ffma2_rn(f2(-kC), A[i], X[i]);
+    const float XJ = (J & 1) ? X[J / 2].y : X[J / 2].x;
+    const float xj = fmaf(XJ, imk1, imk1DX1);
     const float pp = fmaf(w.owi, xj, w.alpha);  // p = alpha + (1-alpha) wi xj
-    const float Ps = pp * sTimk1;
-    const float Qs = fmaf(Ps, DX1, (w.owj * sT * xj) * xj);
-    const float PH = pp * cdsm;
-    float aI = 0.0f, aS = 0.0f;
+    const float ps = pp * sTimk1;
+    const float2 Ps = f2(ps);
+    const float2 Qs = f2(fmaf(ps, DX1, (w.owj * sT * xj) * xj));
+    const float2 PH = f2(pp * cdsm);
+    float2 aI = f2(0.0f), aS = f2(0.0f);
 #pragma unroll
-    for (int i = 0; i < NG; ++i) {
-      const float ts = fmaf(X[i], Ps, Qs);
-      const float r = F::r(ts);
-      A[i] = fmaf(r, cAr, A[i]);
-      G[i] = fmaf(kC, H[i], G[i]);
-      const float gt = F::gt(G[i], ts, r);
-      H[i] = fmaf(gt, PH, H[i]);
-      aI = fmaf(gt, X[i], aI);
-      aS += gt;
+    for (int i = 0; i < NG / 2; ++i) {
+      const float2 ts = __ffma2_rn(X[i], Ps, Qs);
+      const float2 r = F::r(ts);
+      A[i] = __ffma2_rn(r, f2(cAr), A[i]);
+      G[i] = __ffma2_rn(f2(kC), H[i], G[i]);
+      const float2 gt = F::gt(G[i], ts, r);
+      H[i] = __ffma2_rn(gt, PH, H[i]);
+      aI = __ffma2_rn(gt, X[i], aI);
+      aS = __fadd2_rn(aS, gt);
     }
-    const float tI = fmaf(DX1, aS, aI) * cdsm;  // sum_i gT_i x_i
-    const float tS = aS * cdsmk;                // sum_i gT_i
+    const float sS = aS.x + aS.y;
+    const float tI = fmaf(DX1, sS, aI.x + aI.y) * cdsm;  // sum_i gT_i x_i
+    const float tS = sS * cdsmk;                          // sum_i gT_i
     // gx_j += (1-alpha) (wi sum gT x + 2 wj xj sum gT), in units of m^(k+1)
-    H[J] = fmaf(fmaf(w.owi, tI, 2.0f * w.owj * xj * tS), imk1, H[J]);
+    const float add = fmaf(w.owi, tI, 2.0f * w.owj * xj * tS) * imk1;
+    if (J & 1) H[J / 2].y += add; else H[J / 2].x += add;
     const float oxj = w.oma * xj;
     dwi = fmaf(oxj, tI, dwi);
     dwj = fmaf(oxj * xj, tS, dwj);
@@ -412,8 +440,8 @@ struct BwdSteps {
 };
 template <int NG, int ACT>
 struct BwdSteps<NG, ACT, -1> {
-  static __device__ __forceinline__ void run(float (&)[NG], float (&)[NG], float (&)[NG], float (&)[NG], const StageW&,
-                                             float&, float&) {}
+  static __device__ __forceinline__ void run(float2 (&)[NG / 2], float2 (&)[NG / 2], float2 (&)[NG / 2],
+                                             float2 (&)[NG / 2], const StageW&, float&, float&) {}
 };
 
 // On entry (x, a) hold the group's OUTPUT and (gx, ga) the incoming cotangents; on exit the
@@ -421,18 +449,31 @@ struct BwdSteps<NG, ACT, -1> {
 template <int NG, int ACT>
 __device__ __forceinline__ void group_backward(float (&x)[NG], float (&a)[NG], float (&gx)[NG], float (&ga)[NG],
                                                const StageW& w, float& dwi, float& dwj) {
+  static_assert(NG % 2 == 0, "positions are processed in pairs");
   using F = ActForm<ACT>;
-  BwdSteps<NG, ACT, NG - 1>::run(x, a, gx, ga, w, dwi, dwj);
+  float2 X[NG / 2], A[NG / 2], H[NG / 2], G[NG / 2];
+#pragma unroll
+  for (int i = 0; i < NG / 2; ++i) {
+    X[i] = make_float2(x[2 * i], x[2 * i + 1]);
+    A[i] = make_float2(a[2 * i], a[2 * i + 1]);
+    H[i] = make_float2(gx[2 * i], gx[2 * i + 1]);
+    G[i] = make_float2(ga[2 * i], ga[2 * i + 1]);
+  }
+  BwdSteps<NG, ACT, NG - 1>::run(X, A, H, G, w, dwi, dwj);
   constexpr float imN = (float)(1.0 / cpow(kMd, NG));
   constexpr float imNDX = (float)(bwd_DX(NG, F::f0) / cpow(kMd, NG));
   constexpr float imNCA = (float)(bwd_CA(NG, F::f0) / cpow(kMd, NG));
   constexpr float mN = (float)cpow(kMd, NG);
 #pragma unroll
-  for (int i = 0; i < NG; ++i) {
-    x[i] = fmaf(x[i], imN, imNDX);
-    a[i] = fmaf(a[i], imN, imNCA);
-    gx[i] *= mN;
-    ga[i] *= mN;
+  for (int i = 0; i < NG / 2; ++i) {
+    const float2 xo = __ffma2_rn(X[i], f2(imN), f2(imNDX));
+    const float2 ao = __ffma2_rn(A[i], f2(imN), f2(imNCA));
+    const float2 ho = __fmul2_rn(H[i], f2(mN));
+    const float2 go = __fmul2_rn(G[i], f2(mN));
+    x[2 * i] = xo.x; x[2 * i + 1] = xo.y;
+    a[2 * i] = ao.x; a[2 * i + 1] = ao.y;
+    gx[2 * i] = ho.x; gx[2 * i + 1] = ho.y;
+    ga[2 * i] = go.x; ga[2 * i + 1] = go.y;
   }
 }
 
