@@ -71,6 +71,7 @@ static bool rows_shape_ok(int64_t N, int64_t E, int n, int C, int dtype) {
 }
 
 struct Plan {
+  bool pair = false;  // two groups per thread (ncn_pairs.cuh)
   int threads = 0, R = 0, nbuf = 0, grid = 0;
   size_t smem = 0;
   uint32_t off_in[2] = {0, 0}, off_work = 0, off_out = 0, off_ckpt = kNoOff, off_red = 0, off_w = 0, off_bar = 0;
@@ -79,6 +80,24 @@ struct Plan {
 };
 
 typedef cudaError_t (*RowsLaunchFn)(int, int, const RowsParams&, int, int, size_t, cudaStream_t, int*);
+
+static RowsLaunchFn pair_fn(int n, bool bwd) {
+  if (bwd) {
+    switch (n) {
+      case 2: return launch_pair_bwd_n2;
+      case 4: return launch_pair_bwd_n4;
+      case 8: return launch_pair_bwd_n8;
+      default: return nullptr;  // 16: the pair's four streams do not fit the register file
+    }
+  }
+  switch (n) {
+    case 2: return launch_pair_fwd_n2;
+    case 4: return launch_pair_fwd_n4;
+    case 8: return launch_pair_fwd_n8;
+    case 16: return launch_pair_fwd_n16;
+    default: return nullptr;
+  }
+}
 
 static RowsLaunchFn rows_fn(int n, bool bwd) {
   switch (n) {
@@ -96,7 +115,50 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
                      const DevInfo& dev, int act, Plan& pl) {
   const int w = dtype == DT_BF16 ? 2 : 4;
   const int m = N / n;
-  int maxT = rows_max_threads(n, bwd);
+  // fast path: one pair of groups (g, g + m/2) per thread, if a row's pairs fit one CTA
+  const char* nopair = std::getenv("NCN_NO_PAIR");
+  pl.pair = pair_fn(n, bwd) != nullptr && m % 2 == 0 && m / 2 <= pair_max_threads(n, bwd) && !(nopair && nopair[0] == '1');
+  if (pl.pair && bwd) {
+    // pair backward: one 16-byte slot per position doubles as TMA landing zone and output staging
+    const bool residual = (flags & F_RESIDUAL) != 0;
+    const int slots = (flags & F_RECOMPUTE) ? 0 : n_ck;
+    const int maxTp = pair_max_threads(n, true);
+    int Rp = (m / 2) >= maxTp ? 1 : maxTp / (m / 2);
+    if ((int64_t)Rp > B) Rp = (int)B;
+    for (; Rp >= 1; Rp = (Rp > 1 ? Rp / 2 : 0)) {
+      const int threads = (int)align_up((uint32_t)(Rp * (m / 2)), 32);
+      const uint64_t RN = (uint64_t)Rp * N;
+      uint64_t off = 0;
+      auto take = [&](uint64_t bytes) { uint64_t o = off; off = (off + bytes + 127) / 128 * 128; return (uint32_t)o; };
+      pl.off_in[0] = pl.off_in[1] = 0;
+      pl.off_work = take(RN * 16);
+      pl.off_out = pl.off_work;
+      uint64_t ckb = (uint64_t)slots * RN * 8;
+      if (residual && RN * w > ckb) ckb = RN * w;
+      pl.off_ckpt = take(ckb ? ckb : 16);
+      pl.off_red = take((uint64_t)2 * L * (threads / 32) * 4);
+      pl.off_w = take((uint64_t)16 * L);
+      pl.off_bar = take(32);
+      if (off <= (uint64_t)dev.smem_optin) {
+        pl.threads = threads; pl.R = Rp; pl.nbuf = 1; pl.n_ckpt_slots = (uint32_t)slots; pl.smem = (size_t)off;
+        pl.tiles = (B + Rp - 1) / Rp;
+        int occ = 0;
+        RowsParams dummy{};
+        cudaError_t e = pair_fn(n, true)(act, dtype, dummy, 0, pl.threads, pl.smem, nullptr, &occ);
+        if (e != cudaSuccess) return cuda_fail(e);
+        if (occ >= 1) {
+          if (occ > 32) occ = 32;
+          long long grid = (long long)dev.sms * occ;
+          if (grid > pl.tiles) grid = pl.tiles;
+          pl.grid = (int)grid;
+          return NCN_OK;
+        }
+      }
+    }
+    pl.pair = false;  // does not fit: general kernel
+  }
+  const int items = pl.pair ? m / 2 : m;  // work items per row
+  int maxT = pl.pair ? pair_max_threads(n, bwd) : rows_max_threads(n, bwd);
   int force_nbuf = 0;
   if (const char* e = std::getenv(bwd ? "NCN_BWD_THREADS" : "NCN_FWD_THREADS")) {  // tuning experiments
     const int t = std::atoi(e);
@@ -105,12 +167,12 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   if (const char* e = std::getenv("NCN_NBUF")) force_nbuf = std::atoi(e);
   const bool recompute = (flags & F_RECOMPUTE) != 0;
   if (recompute) n_ck = 0;
-  int R = m >= maxT ? 1 : maxT / m;
+  int R = items >= maxT ? 1 : maxT / items;
   if ((int64_t)R > B) R = (int)B;
   const uint32_t limit = (uint32_t)dev.smem_optin;
 
   auto layout = [&](int R_, int nbuf, int slots, Plan& p) -> bool {
-    const int threads = (int)align_up((uint32_t)((int64_t)R_ * m < maxT ? R_ * m : maxT), 32);
+    const int threads = (int)align_up((uint32_t)((int64_t)R_ * items < maxT ? R_ * items : maxT), 32);
     const int nwarp = threads / 32;
     const uint64_t RN = (uint64_t)R_ * N;
     const uint64_t in_b = (bwd ? 4 : 2) * RN * w;
@@ -150,7 +212,7 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   pl.tiles = (B + pl.R - 1) / pl.R;
   int occ = 0;
   RowsParams dummy{};
-  cudaError_t e = rows_fn(n, bwd)(act, dtype, dummy, 0, pl.threads, pl.smem, nullptr, &occ);
+  cudaError_t e = (pl.pair ? pair_fn(n, bwd) : rows_fn(n, bwd))(act, dtype, dummy, 0, pl.threads, pl.smem, nullptr, &occ);
   if (e != cudaSuccess) return cuda_fail(e);
   if (occ < 1) return NCN_ERR_SMEM;
   if (occ > 32) occ = 32;
@@ -332,7 +394,8 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);
-  cudaError_t e = rows_fn(n_cache, false)(act, dtype, p, pl.grid, pl.threads, pl.smem, (cudaStream_t)stream, nullptr);
+  cudaError_t e = (pl.pair ? pair_fn(n_cache, false) : rows_fn(n_cache, false))(act, dtype, p, pl.grid, pl.threads, pl.smem,
+                                                                               (cudaStream_t)stream, nullptr);
   return e == cudaSuccess ? NCN_OK : cuda_fail(e);
 }
 
@@ -372,7 +435,8 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);
-  cudaError_t e = rows_fn(n_cache, true)(act, dtype, p, pl.grid, pl.threads, pl.smem, (cudaStream_t)stream, nullptr);
+  cudaError_t e = (pl.pair ? pair_fn(n_cache, true) : rows_fn(n_cache, true))(act, dtype, p, pl.grid, pl.threads, pl.smem,
+                                                                             (cudaStream_t)stream, nullptr);
   if (e != cudaSuccess) return cuda_fail(e);
   return reduce_dw(p.partials, dW, pl.grid, 2 * L, dw_accumulate, (cudaStream_t)stream);
 }

@@ -1,0 +1,51 @@
+// Explicit instantiation of the pair kernels (ncn_pairs.cuh) for one group size (NCN_NG) and
+// one direction (NCN_BWD defined or not).
+#include "ncn_pairs.cuh"
+#include "ncn_rows_launch.h"
+
+namespace ncn {
+
+#ifdef NCN_BWD
+#define NCN_KERNEL pair_bwd_kernel
+#define NCN_CFG PairLaunch<NCN_NG, true>
+#else
+#define NCN_KERNEL pair_fwd_kernel
+#define NCN_CFG PairLaunch<NCN_NG, false>
+#endif
+
+template <int ACT, typename T>
+static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st, int* occ) {
+  auto k = NCN_KERNEL<NCN_NG, ACT, T, NCN_CFG::threads, NCN_CFG::min_blocks>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, smem);
+  k<<<grid, threads, smem, st>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_act(int act, const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st,
+                              int* occ) {
+  switch (act) {
+    case ACT_TANH: return launch_one<ACT_TANH, T>(p, grid, threads, smem, st, occ);
+    case ACT_RELU: return launch_one<ACT_RELU, T>(p, grid, threads, smem, st, occ);
+    case ACT_SIGMOID: return launch_one<ACT_SIGMOID, T>(p, grid, threads, smem, st, occ);
+    default: return launch_one<ACT_LINEAR, T>(p, grid, threads, smem, st, occ);
+  }
+}
+
+#define NCN_CAT2(a, b) a##b
+#define NCN_CAT(a, b) NCN_CAT2(a, b)
+#ifdef NCN_BWD
+#define NCN_FN NCN_CAT(launch_pair_bwd_n, NCN_NG)
+#else
+#define NCN_FN NCN_CAT(launch_pair_fwd_n, NCN_NG)
+#endif
+
+cudaError_t NCN_FN(int act, int dtype, const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st,
+                   int* occ) {
+  if (dtype == DT_BF16) return launch_act<__nv_bfloat16>(act, p, grid, threads, smem, st, occ);
+  return launch_act<float>(act, p, grid, threads, smem, st, occ);
+}
+
+}  // namespace ncn
