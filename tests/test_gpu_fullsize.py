@@ -1,0 +1,131 @@
+"""Full-size configurations: properties that need no oracle run of the full problem.
+
+* round trip: the backward's rebuilt net input equals the input that was fed to the forward;
+* rows are independent: a slice of a big run equals a run on that slice alone (bit for bit);
+* the row slice is checked against the CPU oracle;
+* dW of the batch equals the sum of dW over its parts.
+"""
+import pytest
+import torch
+
+from oracle import ncn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ncn():
+    import ncn_cuda_b200
+
+    return ncn_cuda_b200
+
+
+def _weights(seed, L, var, dev):
+    g = torch.Generator().manual_seed(seed)
+    return torch.stack([torch.randn(2, generator=g) * var ** 0.5 for _ in range(L)]).to(dev)
+
+
+def _run(ncn, x, xa, dy, dya, W, n, every, recompute=False, want_inputs=False):
+    y, ya, ck = ncn.ops.net_fwd(x, xa, W, 0.9, 0, n, 1, 0, every)
+    if recompute:
+        out = ncn.ops.net_bwd(x, xa, dy, dya, W, 0.9, 0, n, 1, 0, recompute=True, want_inputs=want_inputs)
+    else:
+        out = ncn.ops.net_bwd(y, ya, dy, dya, W, 0.9, 0, n, 1, 0, ckpt=ck, ckpt_every=every, want_inputs=want_inputs)
+    return (y, ya) + tuple(out)
+
+
+@pytest.mark.parametrize("name,B,N,n,L,var,seed,every", [
+    ("cfg2", 65536, 4096, 4, 6, 0.25, 1, 4),
+    ("cfg4_invertible", 131072, 4096, 8, 4, 0.01, 3, 0),
+])
+def test_fp32_full_size(ncn, name, B, N, n, L, var, seed, every):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(B, N, 1, device=dev, generator=g)
+    xa = torch.zeros_like(x)
+    dy = torch.randn(B, N, 1, device=dev, generator=g)
+    dya = torch.randn(B, N, 1, device=dev, generator=g)
+    W = _weights(seed, L, var, dev)
+    y, ya, dx, dxa, dW, xr, xar = _run(ncn, x, xa, dy, dya, W, n, every, want_inputs=True)
+    ncn.ops.device_status()
+    # round trip through forward + reversible backward.  Each rebuilt step grows earlier rounding by
+    # 1/0.9: chains of <= 16 steps (checkpointed) stay near 1e-5 in the worst of 2.7e8 elements, the
+    # 32-step chain of the checkpoint-free variant reaches ~1e-4.
+    rt_tol = 2e-5 if every else 2e-4
+    assert O.rel_err(xr, x) < rt_tol, O.rel_err(xr, x)
+    assert float((xar - xa).abs().max()) < rt_tol * 4
+    # a slice of rows taken from the middle of the batch, run alone
+    lo, hi = B // 2 + 17, B // 2 + 17 + 96
+    sy, sya, sdx, sdxa, sdW = _run(ncn, x[lo:hi].clone(), xa[lo:hi].clone(), dy[lo:hi].clone(), dya[lo:hi].clone(), W, n, every)
+    assert torch.equal(sy, y[lo:hi]) and torch.equal(sya, ya[lo:hi])
+    assert torch.equal(sdx, dx[lo:hi]) and torch.equal(sdxa, dxa[lo:hi])
+    # ... and against the CPU oracle
+    ws = [W[l].cpu() for l in range(L)]
+    ry, rya, rdx, rdxa, rdW = O.net_fwd_bwd(x[lo:hi].cpu(), xa[lo:hi].cpu(), ws, dy[lo:hi].cpu(), dya[lo:hi].cpu(), 0.9, "tanh", n, 1)
+    tol = 1e-5
+    assert O.rel_err(sy, ry) < tol and O.rel_err(sya, rya) < tol
+    assert O.rel_err(sdx, rdx) < tol and O.rel_err(sdxa, rdxa) < tol
+    for l in range(L):
+        assert O.rel_err(sdW[l], rdW[l]) < 2e-5, (l, O.rel_err(sdW[l], rdW[l]))
+    # dW is additive over parts of the batch
+    acc = torch.zeros_like(dW)
+    q = B // 4
+    for k in range(4):
+        part = _run(ncn, x[k * q:(k + 1) * q], xa[k * q:(k + 1) * q], dy[k * q:(k + 1) * q], dya[k * q:(k + 1) * q], W, n, every)
+        acc += part[4]
+    assert O.rel_err(acc, dW) < 1e-5
+    # and bitwise reproducible
+    again = _run(ncn, x, xa, dy, dya, W, n, every)
+    assert torch.equal(again[4], dW) and torch.equal(again[2], dx)
+
+
+def test_bf16_beyond_2_31_elements(ncn):
+    """262144 x 8192 bf16 rows (+64) put the last rows past element 2^31: 64-bit addressing."""
+    dev = torch.device("cuda")
+    B, N, n, L = 262144 + 64, 8192, 16, 4
+    g = torch.Generator(device=dev).manual_seed(2)
+    x = torch.empty(B, N, 1, device=dev, dtype=torch.bfloat16)
+    dy = torch.empty_like(x)
+    step = 32768
+    for b in range(0, B, step):  # fill in pieces: no fp32 copy of the whole tensor
+        e = min(B, b + step)
+        x[b:e] = torch.randn(e - b, N, 1, device=dev, generator=g).bfloat16()
+        dy[b:e] = torch.randn(e - b, N, 1, device=dev, generator=g).bfloat16()
+    xa = torch.zeros_like(x)
+    dya = torch.zeros_like(x)
+    W = _weights(2, L, 1 / 16, dev)
+    y, ya, dx, dxa, dW = _run(ncn, x, xa, dy, dya, W, n, 0, recompute=True)
+    ncn.ops.device_status()
+    assert x.numel() > 2 ** 31
+    lo, hi = B - 48, B
+    sy, sya, sdx, sdxa, sdW = _run(ncn, x[lo:hi].clone(), xa[lo:hi].clone(), dy[lo:hi].clone(), dya[lo:hi].clone(), W, n, 0, recompute=True)
+    assert torch.equal(sy, y[lo:hi]) and torch.equal(sdx, dx[lo:hi]) and torch.equal(sdxa, dxa[lo:hi])
+    ws = [W[l].cpu() for l in range(L)]
+    ry, rya, rdx, rdxa, _ = O.net_fwd_bwd(x[lo:hi].float().cpu(), xa[lo:hi].float().cpu(), ws, dy[lo:hi].float().cpu(),
+                                          dya[lo:hi].float().cpu(), 0.9, "tanh", n, 1)
+    assert O.rel_err(sy.float(), ry) < 2e-2 and O.rel_err(sya.float(), rya) < 2e-2
+    assert O.rel_err(sdx.float(), rdx) < 2e-2 and O.rel_err(sdxa.float(), rdxa) < 2e-2
+    assert torch.isfinite(dW).all()
+
+
+def test_residual_stack_bf16_slice(ncn):
+    """The 12-layer residual stack (D = 2048, g = 8, 4 stages per layer, bf16) on a slice of rows."""
+    dev = torch.device("cuda")
+    layers, L, n, N, B = 12, 4, 8, 2048, 4096
+    torch.manual_seed(4)
+    stack = ncn.NCNResidualStack(layers, 0.9, "tanh", n, 1, L, 1, w_std=(1 / 8) ** 0.5).to(dev)
+    x = torch.randn(B, N, 1, device=dev).bfloat16().requires_grad_()
+    xa = torch.zeros(B, N, 1, device=dev, dtype=torch.bfloat16).requires_grad_()
+    dy = torch.randn(B, N, 1, device=dev).bfloat16()
+    y, ya = stack(x, xa)
+    torch.autograd.backward([y, ya], [dy, torch.zeros_like(dy)])
+    ncn.ops.device_status()
+    rows = 16
+    W = stack.weight.detach().cpu()
+    lws = [[W[k, l] for l in range(L)] for k in range(layers)]
+    ry, rya, rdx, rdxa, _ = O.stack_fwd_bwd(x[:rows].detach().float().cpu(), xa[:rows].detach().float().cpu(), lws,
+                                            dy[:rows].float().cpu(), torch.zeros(rows, N, 1), 0.9, "tanh", n, 1)
+    # bf16 rounding of 12 stored layer boundaries accumulates: 2e-2 per tensor is the stated bound
+    assert O.rel_err(y[:rows].float(), ry) < 2e-2 and O.rel_err(ya[:rows].float(), rya) < 2e-2
+    assert O.rel_err(x.grad[:rows].float(), rdx) < 2e-2 and O.rel_err(xa.grad[:rows].float(), rdxa) < 2e-2
+    assert torch.isfinite(stack.weight.grad).all()
