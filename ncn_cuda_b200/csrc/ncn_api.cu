@@ -204,7 +204,10 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
     if (bwd && n_ck > 0) {
       ok = layout(R, 1, n_ck, pl) || layout(R, 1, 0, pl);
     } else {
-      ok = (force_nbuf != 1 && layout(R, 2, 0, pl)) || layout(R, 1, 0, pl);
+      // pair forward: a single input buffer leaves room for a second CTA on the SM, whose stages
+      // overlap this one's stage boundaries; that is worth more than the earlier prefetch
+      const bool prefer_one = pl.pair && !bwd && force_nbuf != 2;
+      ok = (force_nbuf != 1 && !prefer_one && layout(R, 2, 0, pl)) || layout(R, 1, 0, pl);
     }
     if (ok) break;
   }
