@@ -44,7 +44,8 @@ enum {
   NCN_ERR_WORKSPACE = 6,   /* workspace missing or smaller than ncn_bwd_workspace_bytes() */
   NCN_ERR_CUDA = 7,        /* a CUDA runtime call failed; see ncn_last_cuda_error() */
   NCN_ERR_NULL = 8,        /* a required pointer is null */
-  NCN_ERR_DEVICE_WAIT = 9  /* (ncn_device_status) a kernel gave up a bounded wait on a copy */
+  NCN_ERR_DEVICE_WAIT = 9, /* (ncn_device_status) a kernel gave up a bounded wait on a copy */
+  NCN_ERR_TOO_LARGE = 10   /* (ncn_net_bwd_noalloc) more scratch needed than the built-in array holds */
 };
 
 /* flags of the net calls */
@@ -87,6 +88,28 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
                 void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, void* workspace,
                 size_t workspace_bytes, int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module,
                 int L, double alpha, int activation, int dtype, int flags, int dw_accumulate, void* stream);
+
+/* ncn_net_bwd for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts of this operator get no chance to reserve a workspace: a plugin whose
+ * host hands it only the input and output tensors, a control loop that must never touch the
+ * allocator because allocation may synchronise the device, code that runs after the application
+ * has frozen its memory budget.  For them the scratch of the backward kernel (one row of 2L
+ * partial weight-gradient sums per CTA) lives in a 64 KiB array inside the library image; every
+ * GPU that loads the library carries that array until the process exits.
+ *  - Arguments and results are those of ncn_net_bwd without workspace / workspace_bytes; results
+ *    are bitwise those of ncn_net_bwd for equal arguments.
+ *  - Limit: CTAs launched x 2L <= 16384 floats (on a 148-SM part with two CTAs per SM: L <= 27);
+ *    beyond it the call returns NCN_ERR_TOO_LARGE and enqueues nothing.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current); make that first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the last call's partial sums.  Nothing
+ *    in it has to be cleared (the kernel writes every element the reduction reads), but two calls
+ *    whose kernels overlap on the GPU (different streams, no ordering) race on it: order them. */
+int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx,
+                        void* dxa, void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, int64_t B,
+                        int64_t N, int64_t E, int n_cache, int n_head, int first_module, int L, double alpha,
+                        int activation, int dtype, int flags, int dw_accumulate, void* stream);
 
 /* 1 if ncn_net_fwd / ncn_net_bwd cover these arguments on the current device, else 0. */
 int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype, int flags,

@@ -35,6 +35,10 @@ SIGNATURES = {
         + [c_int] * 4
         + [c_double, c_int, c_int, c_int, c_int, c_void_p],
     ),
+    "ncn_net_bwd_noalloc": (
+        c_int,
+        [c_void_p] * 10 + [c_void_p, c_int] + [c_int64] * 3 + [c_int] * 4 + [c_double, c_int, c_int, c_int, c_int, c_void_p],
+    ),
     "ncn_net_supported": (c_int, [c_int64] * 3 + [c_int] * 6),
     "ncn_bwd_workspace_bytes": (c_size_t, [c_int64] * 3 + [c_int] * 4),
     "ncn_ckpt_bytes": (c_size_t, [c_int64] * 3 + [c_int] * 2),

@@ -327,6 +327,7 @@ const char* ncn_status_string(int s) {
     case NCN_ERR_CUDA: return "CUDA runtime error";
     case NCN_ERR_NULL: return "null pointer";
     case NCN_ERR_DEVICE_WAIT: return "a kernel abandoned a bounded wait on an asynchronous copy";
+    case NCN_ERR_TOO_LARGE: return "problem needs more scratch than the fixed array of ncn_net_bwd_noalloc holds";
     default: return "unknown status";
   }
 }
@@ -518,3 +519,86 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Backward entry point that allocates nothing (declared in include/ncn_b200.h).
+//
+// The backward kernel needs scratch memory for its per-CTA weight-gradient partials.  The
+// other entry points take that scratch from the caller; this one keeps it in the library
+// image, for callers that have no way to obtain device memory where they call from.
+namespace ncn {
+
+constexpr size_t kNoAllocFloats = 16384;  // 64 KiB per device that loads the library
+
+// File-scope device array.  In host code this NAME is only a handle for the runtime's symbol
+// table, not a device address: the address is looked up with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+// Device address of the array on the current device, looked up once per device.
+static int noalloc_scratch(float** out) {
+  static float* table[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= 64) return NCN_ERR_CUDA;
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (ptr == nullptr) return NCN_ERR_CUDA;
+    table[dev] = ptr;
+    ready[dev].store(1, std::memory_order_release);
+  }
+  *out = table[dev];
+  return NCN_OK;
+}
+
+}  // namespace ncn
+
+extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* dy, const void* dya, const float* W,
+                                   void* dx, void* dxa, void* x_rec, void* xa_rec, float* dW, const float* ckpt,
+                                   int ckpt_every, int64_t B, int64_t N, int64_t E, int n_cache, int n_head,
+                                   int first_module, int L, double alpha, int activation, int dtype, int flags,
+                                   int dw_accumulate, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
+  if (!s0 || !s1 || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
+  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
+  if ((flags & F_RESIDUAL) && !(flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
+  if (!aligned16(s0) || !aligned16(s1) || !aligned16(dy) || !aligned16(dya) || !aligned16(dx) || !aligned16(dxa) ||
+      (x_rec && (!aligned16(x_rec) || !aligned16(xa_rec))) || (ckpt && !aligned16(ckpt)))
+    return NCN_ERR_ALIGN;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  float* scratch = nullptr;
+  if ((rc = noalloc_scratch(&scratch)) != NCN_OK) return rc;
+  const int act = map_act(activation);
+  const bool use_ck = ckpt && ckpt_every > 0 && !(flags & F_RECOMPUTE) && (L - 1) / ckpt_every > 0;
+  const int n_ck = use_ck ? (L - 1) / ckpt_every : 0;
+  Plan pl;
+  if ((rc = plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, x_rec != nullptr, dev, act, pl)) != NCN_OK)
+    return rc;
+  // one row of 2L partial sums per CTA must fit the fixed array
+  if ((size_t)pl.grid * 2 * (size_t)L > kNoAllocFloats) return NCN_ERR_TOO_LARGE;
+  RowsParams p{};
+  p.in[0] = s0; p.in[1] = s1; p.in[2] = dy; p.in[3] = dya;
+  p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
+  p.ckpt = use_ck ? const_cast<float*>(ckpt) : nullptr;
+  p.ckpt_every = ckpt_every;
+  p.W = W;
+  p.partials = scratch;  // every element the reduction reads is written by the kernel first
+  p.status = dev.status;
+  p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
+  p.flags = flags & (F_RESIDUAL | F_RECOMPUTE);
+  p.alpha = (float)alpha;
+  p.oma = (float)(1.0 - alpha);
+  fill_offsets(p, pl);
+  cudaError_t e = (pl.pair ? pair_fn(n_cache, true) : rows_fn(n_cache, true))(act, dtype, p, pl.grid, pl.threads, pl.smem,
+                                                                             (cudaStream_t)stream, nullptr);
+  if (e != cudaSuccess) return cuda_fail(e);
+  return reduce_dw(p.partials, dW, pl.grid, 2 * L, dw_accumulate, (cudaStream_t)stream);
+}
+
