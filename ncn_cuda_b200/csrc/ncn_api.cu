@@ -49,6 +49,15 @@ static int get_dev(DevInfo& out) {
   return NCN_OK;
 }
 
+// tanh with bf16 storage runs on tanh.approx inside the fused kernels (NCN_EXACT_TANH=1 turns that off)
+static int fused_act(int act, int dtype) {
+  if (act == ACT_TANH && dtype == DT_BF16) {
+    const char* e = std::getenv("NCN_EXACT_TANH");
+    if (!(e && e[0] == '1')) return ACT_TANH_FAST;
+  }
+  return act;
+}
+
 static int map_act(int code) {
   switch (code) {
     case 0: return ACT_TANH;
@@ -72,6 +81,8 @@ static bool rows_shape_ok(int64_t N, int64_t E, int n, int C, int dtype) {
 
 struct Plan {
   bool pair = false;  // two groups per thread (ncn_pairs.cuh)
+  bool red_thread = false;  // dW partial slots per thread
+  int variant = 0;    // pair backward: 0 aliased tile buffer, 1 separate buffers
   int threads = 0, R = 0, nbuf = 0, grid = 0;
   size_t smem = 0;
   uint32_t off_in[2] = {0, 0}, off_work = 0, off_out = 0, off_ckpt = kNoOff, off_red = 0, off_w = 0, off_bar = 0;
@@ -111,14 +122,16 @@ static RowsLaunchFn rows_fn(int n, bool bwd) {
 
 // Lay the tile out in shared memory.  Preference: two input buffers (prefetch of the next tile
 // starts a whole tile early) > checkpoints staged in shared memory > one input buffer.
-static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
-                     const DevInfo& dev, int act, Plan& pl) {
+static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
+                          const DevInfo& dev, int act, bool want_wide, Plan& pl) {
   const int w = dtype == DT_BF16 ? 2 : 4;
   const int m = N / n;
   // fast path: one pair of groups (g, g + m/2) per thread, if a row's pairs fit one CTA
   const char* nopair = std::getenv("NCN_NO_PAIR");
   pl.pair = pair_fn(n, bwd) != nullptr && m % 2 == 0 && m / 2 <= pair_max_threads(n, bwd) && !(nopair && nopair[0] == '1');
-  if (pl.pair && bwd) {
+  const bool wide = bwd && pl.pair && want_wide;
+  if (wide) pl.variant = 1;  // separate buffers: planned by the general layout below
+  if (pl.pair && bwd && !wide) {
     // pair backward: one 16-byte slot per position doubles as TMA landing zone and output staging
     const bool residual = (flags & F_RESIDUAL) != 0;
     const int slots = (flags & F_RECOMPUTE) ? 0 : n_ck;
@@ -187,7 +200,12 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
     p.off_work = take(work_b);
     p.off_out = take(out_b);
     p.off_ckpt = slots ? take(ck_b) : kNoOff;
-    p.off_red = take(bwd ? (uint64_t)2 * L * nwarp * 4 : 0);
+    const uint64_t red_warp = bwd ? (uint64_t)2 * L * nwarp * 4 : 0;
+    const uint64_t red_thr = (uint64_t)2 * L * threads * 4;
+    const uint64_t fixed_rest = 16ull * L + 32 + 512;
+    const bool rt = bwd && pl.pair && pl.variant == 1 && off + red_thr + fixed_rest <= limit;
+    p.red_thread = rt;
+    p.off_red = take(rt ? red_thr : red_warp);
     p.off_w = take((uint64_t)16 * L);  // one StageRec per stage
     p.off_bar = take(32);
     if (off > limit) return false;
@@ -215,6 +233,7 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   pl.tiles = (B + pl.R - 1) / pl.R;
   int occ = 0;
   RowsParams dummy{};
+  dummy.variant = pl.variant;
   cudaError_t e = (pl.pair ? pair_fn(n, bwd) : rows_fn(n, bwd))(act, dtype, dummy, 0, pl.threads, pl.smem, nullptr, &occ);
   if (e != cudaSuccess) return cuda_fail(e);
   if (occ < 1) return NCN_ERR_SMEM;
@@ -223,6 +242,25 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   if (grid > pl.tiles) grid = pl.tiles;
   pl.grid = (int)grid;
   return NCN_OK;
+}
+
+// Pair backward: the variant with separate buffers (one CTA per SM, full register budget, next
+// tile prefetched) measured slightly faster than the aliased one (two CTAs per SM) and is tried
+// first; NCN_BWD_WIDE=0 forces the aliased variant.
+static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
+                     const DevInfo& dev, int act, Plan& pl) {
+  const char* wide_env = std::getenv("NCN_BWD_WIDE");
+  const bool allow_wide = !(wide_env && wide_env[0] == '0');
+  if (bwd && allow_wide) {
+    Plan trial;
+    const int rc = plan_rows_impl(true, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, true, trial);
+    if (rc == NCN_OK) {
+      pl = trial;
+      return rc;
+    }
+  }
+  pl = Plan();
+  return plan_rows_impl(bwd, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, false, pl);
 }
 
 static void fill_offsets(RowsParams& p, const Plan& pl) {
@@ -235,6 +273,7 @@ static void fill_offsets(RowsParams& p, const Plan& pl) {
   p.off_w = pl.off_w;
   p.off_bar = pl.off_bar;
   p.n_ckpt_slots = pl.n_ckpt_slots;
+  p.variant = pl.variant;
   p.R = pl.R;
   p.nbuf = pl.nbuf;
   p.tiles = pl.tiles;
@@ -383,7 +422,7 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
     return NCN_ERR_ALIGN;
   DevInfo dev;
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
-  const int act = map_act(activation);
+  const int act = fused_act(map_act(activation), dtype);
   Plan pl;
   if ((rc = plan_rows(false, B, (int)N, n_cache, L, dtype, flags, 0, false, dev, act, pl)) != NCN_OK) return rc;
   RowsParams p{};
@@ -420,7 +459,7 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
   DevInfo dev;
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
   if (!workspace || workspace_bytes < workspace_floats(dev, E, L) * sizeof(float)) return NCN_ERR_WORKSPACE;
-  const int act = map_act(activation);
+  const int act = fused_act(map_act(activation), dtype);
   const bool use_ck = ckpt && ckpt_every > 0 && !(flags & F_RECOMPUTE) && (L - 1) / ckpt_every > 0;
   const int n_ck = use_ck ? (L - 1) / ckpt_every : 0;
   Plan pl;
@@ -435,7 +474,7 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
   p.partials = static_cast<float*>(workspace);
   p.status = dev.status;
   p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
-  p.flags = flags & (F_RESIDUAL | F_RECOMPUTE);
+  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE)) | (pl.red_thread ? F_RED_THREAD : 0);
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);
@@ -575,7 +614,7 @@ extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* d
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
   float* scratch = nullptr;
   if ((rc = noalloc_scratch(&scratch)) != NCN_OK) return rc;
-  const int act = map_act(activation);
+  const int act = fused_act(map_act(activation), dtype);
   const bool use_ck = ckpt && ckpt_every > 0 && !(flags & F_RECOMPUTE) && (L - 1) / ckpt_every > 0;
   const int n_ck = use_ck ? (L - 1) / ckpt_every : 0;
   Plan pl;
@@ -592,7 +631,7 @@ extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* d
   p.partials = scratch;  // every element the reduction reads is written by the kernel first
   p.status = dev.status;
   p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
-  p.flags = flags & (F_RESIDUAL | F_RECOMPUTE);
+  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE)) | (pl.red_thread ? F_RED_THREAD : 0);
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);

@@ -18,13 +18,16 @@ constexpr float kC = 0.1f;  // fp32(1 - 0.9)
 constexpr float kInvM = 1.0f / 0.9f;
 constexpr float kCoverM = 0.1f / 0.9f;
 
-enum Act : int { ACT_TANH = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_LINEAR = 3 };
+// ACT_TANH_FAST is internal: tanh through the one-instruction tanh.approx.f32 (relative error 2^-11),
+// used for bf16 storage, whose 2e-2 tolerance it does not threaten; it halves the special-function work.
+enum Act : int { ACT_TANH = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_LINEAR = 3, ACT_TANH_FAST = 4 };
 enum DType : int { DT_F32 = 0, DT_BF16 = 1 };
 
 // flags of the fused row kernels
 enum : int {
   F_RESIDUAL = 1,   // forward: y = x + net(x); backward: dx = dx_net + dy
   F_RECOMPUTE = 2,  // backward: inputs are the net INPUT; replay the forward, then walk back
+  F_RED_THREAD = 4, // backward (set by the launch plan): dW partial slots per thread instead of per warp
 };
 
 // error codes stored in the device status word by a kernel that gave up a wait
@@ -86,6 +89,11 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float rcp_approx(float x) {
@@ -278,6 +286,14 @@ struct ActForm<ACT_SIGMOID> {  // 1 / (1 + 2^(-log2e T)) ; F' = F (1 - F)
   static constexpr double sT = -1.4426950408889634, f0 = 0.0, f1 = 1.0, ds = 1.0;
   static __device__ __forceinline__ float2 r(float2 ts) { return ActForm<ACT_TANH>::r(ts); }
   static __device__ __forceinline__ float2 gt(float2 g, float2 ts, float2 r) { return ActForm<ACT_TANH>::gt(g, ts, r); }
+};
+template <>
+struct ActForm<ACT_TANH_FAST> {  // F = tanh.approx(T) ; F' = 1 - F^2
+  static constexpr double sT = 1.0, f0 = 0.0, f1 = 1.0, ds = 1.0;
+  static __device__ __forceinline__ float2 r(float2 ts) { return make_float2(tanh_approx(ts.x), tanh_approx(ts.y)); }
+  static __device__ __forceinline__ float2 gt(float2 g, float2, float2 r) {
+    return __fmul2_rn(g, __ffma2_rn(make_float2(-r.x, -r.y), r, f2(1.0f)));
+  }
 };
 template <>
 struct ActForm<ACT_RELU> {
@@ -492,6 +508,7 @@ struct RowsParams {
   uint32_t off_in[2];  // byte offsets into dynamic shared memory
   uint32_t off_work, off_out, off_ckpt, off_red, off_w, off_bar;
   uint32_t n_ckpt_slots;  // checkpoints staged in shared memory per tile (0 = read them from global)
+  int variant;            // pair backward: 0 = aliased tile buffer (two CTAs per SM), 1 = separate buffers
 };
 
 constexpr uint32_t kNoOff = 0xFFFFFFFFu;

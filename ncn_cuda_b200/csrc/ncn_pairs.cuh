@@ -552,4 +552,260 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_bwd_kernel(const RowsParams p
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Backward, wide variant: separate input, slot and output buffers (as rows_bwd_kernel), so the next
+// tile's TMA loads run during this tile's stages and no layout change needs a read-barrier-write.
+// One CTA of up to 512 threads per SM with a full register budget (no spills); the aliased kernel
+// above trades registers for a second CTA per SM.
+template <int NG, int ACT, typename T, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) pair_bwd_wide_kernel(const RowsParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  using F = ActForm<ACT>;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarp = (nthr + 31) >> 5;
+  const int N = p.N, m = p.m, R = p.R, L = p.L;
+  const int mh = m >> 1;
+  const int RN = R * N;
+  T* in_s = reinterpret_cast<T*>(smem + p.off_in[0]);
+  const uint32_t work_addr = smem_u32(smem + p.off_work);
+  T* odx = reinterpret_cast<T*>(smem + p.off_out);
+  float2* sck = p.n_ckpt_slots ? reinterpret_cast<float2*>(smem + p.off_ckpt) : nullptr;
+  float* red = reinterpret_cast<float*>(smem + p.off_red);
+  StageRec* recs = reinterpret_cast<StageRec*>(smem + p.off_w);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + p.off_bar);
+  int* abort_flag = reinterpret_cast<int*>(bar + 2);
+  const T* g_in[4] = {static_cast<const T*>(p.in[0]), static_cast<const T*>(p.in[1]), static_cast<const T*>(p.in[2]),
+                      static_cast<const T*>(p.in[3])};
+  const float2* ckpt = reinterpret_cast<const float2*>(p.ckpt);
+  const bool residual = (p.flags & F_RESIDUAL) != 0;
+  const bool recompute = (p.flags & F_RECOMPUTE) != 0;
+  const bool want_rec = p.out[2] != nullptr;
+  const long long BN = p.B * (long long)N;
+  const bool ck_smem = p.n_ckpt_slots > 0;
+
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  fill_stage_table(recs, p, ckpt != nullptr && !recompute, tid, nthr);
+  // weight-gradient partials: one (dwi, dwj) slot per stage and THREAD when they fit (a private
+  // read-modify-write per stage, no shuffles), else one per stage and warp
+  const bool red_thread = (p.flags & F_RED_THREAD) != 0;
+  float2* red2 = reinterpret_cast<float2*>(red);
+  for (int i = tid; i < (red_thread ? 2 * L * nthr : 2 * L * nwarp); i += nthr) red[i] = 0.0f;
+  __syncthreads();
+
+  auto issue_load = [&](long long tl) {
+    const long long row0 = tl * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
+    mbar_expect_tx(&bar[0], 4 * bytes);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) bulk_g2s(in_s + q * RN, g_in[q] + row0 * N, bytes, &bar[0]);
+  };
+  auto issue_ckpt = [&](long long tl) {
+    const long long row0 = tl * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    const uint32_t cbytes = (uint32_t)(rows * N * sizeof(float2));
+    mbar_expect_tx(&bar[1], p.n_ckpt_slots * cbytes);
+    for (uint32_t k = 0; k < p.n_ckpt_slots; ++k)
+      bulk_g2s(sck + k * RN, ckpt + (long long)k * BN + row0 * N, cbytes, &bar[1]);
+  };
+
+  long long tile = blockIdx.x;
+  if (tid == 0 && tile < p.tiles) {
+    issue_load(tile);
+    if (ck_smem) issue_ckpt(tile);
+  }
+  uint32_t phase0 = 0, phase1 = 0;
+  const int r = tid / mh, t = tid - r * mh;
+  const int base = r * N;
+  const uint32_t wrow = work_addr + ((uint32_t)base << 4);
+  constexpr float sT = (float)F::sT;
+  PairWB w;
+  w.alpha = f2(p.alpha);
+  w.oma = f2(p.oma);
+  PairW wf;
+  wf.alpha = f2(p.alpha * sT);
+
+  for (; tile < p.tiles; tile += gridDim.x) {
+    const long long next = tile + gridDim.x;
+    if (!mbar_wait_bounded(&bar[0], phase0)) *abort_flag = 1;
+    phase0 ^= 1;
+    if (ck_smem) {
+      if (!mbar_wait_bounded(&bar[1], phase1)) *abort_flag = 1;
+      phase1 ^= 1;
+    }
+    if (L == 1 && tid == 0) bulk_wait_read0();
+    __syncthreads();
+    if (*abort_flag) break;
+
+    const long long row0 = tile * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    const bool active = r < rows;
+    const T* s0 = in_s + base;
+
+    float2 X[NG], A[NG], H[NG], G[NG];
+    uint32_t aa[NG], ab[NG];
+
+    if (recompute) {
+      for (int l = 0; l < L; ++l) {
+        const StageRec rec = recs[l];
+        const int s = rec.s;
+        wf.owi = f2(rec.owi * sT);
+        wf.owj = f2(rec.owj * sT);
+        if (active) {
+          pair_addrs<NG, 4>(wrow, t, s, m, aa, ab);
+          if (l == 0) {
+            ld_native_pair<NG, T>(s0, t, s, m, X);
+            ld_native_pair<NG, T>(s0 + RN, t, s, m, A);
+          } else {
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              const float2 va = lds64(aa[o]), vb = lds64(ab[o]);
+              X[o] = make_float2(va.x, vb.x);
+              A[o] = make_float2(va.y, vb.y);
+            }
+          }
+          pair_forward<NG, ACT>(X, A, wf);
+#pragma unroll
+          for (int o = 0; o < NG; ++o) {
+            sts64(aa[o], X[o].x, A[o].x);
+            sts64(ab[o], X[o].y, A[o].y);
+          }
+        }
+        __syncthreads();
+      }
+    }
+
+    StageRec rec_next = recs[L - 1];
+    for (int l = L - 1; l >= 0; --l) {
+      const StageRec rec = rec_next;
+      if (l > 0) rec_next = recs[l - 1];  // in flight during this stage's work
+      const int s = rec.s;
+      const bool first = (l == L - 1), last = (l == 0);
+      w.owi = f2(rec.owi);
+      w.owj = f2(rec.owj);
+      w.owjs = f2(rec.owj * sT);
+      float2 dwi = f2(0.0f), dwj = f2(0.0f);
+
+      if (active) {
+        pair_addrs<NG, 4>(wrow, t, s, m, aa, ab);
+        if (first) {
+          ld_native_pair<NG, T>(s0 + 2 * RN, t, s, m, H);
+          ld_native_pair<NG, T>(s0 + 3 * RN, t, s, m, G);
+          if (!recompute) {
+            ld_native_pair<NG, T>(s0, t, s, m, X);
+            ld_native_pair<NG, T>(s0 + RN, t, s, m, A);
+          } else {
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              const float2 va = lds64(aa[o]), vb = lds64(ab[o]);
+              X[o] = make_float2(va.x, vb.x);
+              A[o] = make_float2(va.y, vb.y);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int o = 0; o < NG; ++o) {
+            const float4 va = lds128(aa[o]), vb = lds128(ab[o]);
+            X[o] = make_float2(va.x, vb.x);
+            A[o] = make_float2(va.y, vb.y);
+            H[o] = make_float2(va.z, vb.z);
+            G[o] = make_float2(va.w, vb.w);
+          }
+          if (rec.ck >= 0) {
+            if ((uint32_t)rec.ck < p.n_ckpt_slots) {
+              const float2* c = sck + rec.ck * RN + base + t;
+#pragma unroll
+              for (int o = 0; o < NG; ++o) {
+                const float2 va = c[o * m], vb = c[o * m + mh];
+                X[o] = make_float2(va.x, vb.x);
+                A[o] = make_float2(va.y, vb.y);
+              }
+            } else {
+              const float2* c = ckpt + (long long)rec.ck * BN + row0 * N + base + t;
+#pragma unroll
+              for (int o = 0; o < NG; ++o) {
+                const float2 va = __ldg(c + o * m), vb = __ldg(c + o * m + mh);
+                X[o] = make_float2(va.x, vb.x);
+                A[o] = make_float2(va.y, vb.y);
+              }
+            }
+          }
+        }
+        pair_backward<NG, ACT>(X, A, H, G, w, dwi, dwj);
+        if (last) {
+          if (residual) {
+            float2 gin[NG];
+            ld_native_pair<NG, T>(s0 + 2 * RN, t, s, m, gin);
+#pragma unroll
+            for (int o = 0; o < NG; ++o) H[o] = fadd2(H[o], gin[o]);
+          }
+          T* wout = odx + base;
+          st_native_pair<NG, T>(wout, t, s, m, H);
+          st_native_pair<NG, T>(wout + RN, t, s, m, G);
+          if (want_rec) {
+            st_native_pair<NG, T>(wout + 2 * RN, t, s, m, X);
+            st_native_pair<NG, T>(wout + 3 * RN, t, s, m, A);
+          }
+        } else {
+#pragma unroll
+          for (int o = 0; o < NG; ++o) {
+            sts128(aa[o], X[o].x, A[o].x, H[o].x, G[o].x);
+            sts128(ab[o], X[o].y, A[o].y, H[o].y, G[o].y);
+          }
+        }
+      }
+      if (red_thread) {
+        float2 acc = red2[l * nthr + tid];
+        acc.x += dwi.x + dwi.y;
+        acc.y += dwj.x + dwj.y;
+        red2[l * nthr + tid] = acc;
+      } else {
+        const float di = dwi.x + dwi.y, dj = dwj.x + dwj.y;
+        const bool hi = (lane & 16) != 0;
+        const float give = hi ? di : dj;
+        float keep = hi ? dj : di;
+        keep += __shfl_xor_sync(0xffffffffu, give, 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+        if ((lane & 15) == 0) red[(l * nwarp + warp) * 2 + (hi ? 1 : 0)] += keep;
+      }
+      if (l == 1 && tid == 0) bulk_wait_read0();
+      if (last) fence_proxy_async();
+      __syncthreads();
+      if (tid == 0 && next < p.tiles && (residual ? last : first)) issue_load(next);
+      if (ck_smem && tid == 0 && next < p.tiles && l == p.ckpt_every - 1) issue_ckpt(next);
+    }
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
+      bulk_s2g(static_cast<T*>(p.out[0]) + row0 * N, odx, bytes);
+      bulk_s2g(static_cast<T*>(p.out[1]) + row0 * N, odx + RN, bytes);
+      if (want_rec) {
+        bulk_s2g(static_cast<T*>(p.out[2]) + row0 * N, odx + 2 * RN, bytes);
+        bulk_s2g(static_cast<T*>(p.out[3]) + row0 * N, odx + 3 * RN, bytes);
+      }
+      bulk_commit();
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < 2 * L; i += nthr) {
+    const int l = i >> 1, c = i & 1;
+    float acc = 0.0f;
+    if (red_thread) {
+      for (int k = 0; k < nthr; ++k) acc += red[(l * nthr + k) * 2 + c];  // thread order: fixed
+    } else {
+      for (int w2 = 0; w2 < nwarp; ++w2) acc += red[(l * nwarp + w2) * 2 + c];
+    }
+    p.partials[(long long)blockIdx.x * 2 * L + i] = acc;
+  }
+  if (tid == 0) {
+    bulk_wait_all0();
+    if (*abort_flag) atomicExch(p.status, DEV_WAIT_TIMEOUT);
+  }
+}
+
 }  // namespace ncn

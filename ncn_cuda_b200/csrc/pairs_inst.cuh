@@ -15,6 +15,16 @@ namespace ncn {
 
 template <int ACT, typename T>
 static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st, int* occ) {
+#ifdef NCN_BWD
+  if (p.variant == 1) {
+    auto kw = pair_bwd_wide_kernel<NCN_NG, ACT, T, NCN_CFG::threads>;
+    cudaError_t ew = cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ew != cudaSuccess) return ew;
+    if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kw, threads, smem);
+    kw<<<grid, threads, smem, st>>>(p);
+    return cudaGetLastError();
+  }
+#endif
   auto k = NCN_KERNEL<NCN_NG, ACT, T, NCN_CFG::threads, NCN_CFG::min_blocks>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
@@ -26,6 +36,9 @@ static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t
 template <typename T>
 static cudaError_t launch_act(int act, const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st,
                               int* occ) {
+  if constexpr (sizeof(T) == 2) {  // bf16 storage only
+    if (act == ACT_TANH_FAST) return launch_one<ACT_TANH_FAST, T>(p, grid, threads, smem, st, occ);
+  }
   switch (act) {
     case ACT_TANH: return launch_one<ACT_TANH, T>(p, grid, threads, smem, st, occ);
     case ACT_RELU: return launch_one<ACT_RELU, T>(p, grid, threads, smem, st, occ);

@@ -27,6 +27,9 @@ static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t
 template <typename T>
 static cudaError_t launch_act(int act, const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st,
                               int* occ) {
+  if constexpr (sizeof(T) == 2) {  // bf16 storage only
+    if (act == ACT_TANH_FAST) return launch_one<ACT_TANH_FAST, T>(p, grid, threads, smem, st, occ);
+  }
   switch (act) {
     case ACT_TANH: return launch_one<ACT_TANH, T>(p, grid, threads, smem, st, occ);
     case ACT_RELU: return launch_one<ACT_RELU, T>(p, grid, threads, smem, st, occ);
