@@ -35,6 +35,8 @@ WORKLOADS = {
                  desc="invertible variant fp32 x[131072,4096] g=8 4 stages"),
     "cfg3": dict(B=262144, N=8192, n=16, L=4, w_var=1 / 16, dtype="bf16", act="tanh", seed=2,
                  desc="bf16 storage x[262144,8192] g=16 4 stages"),
+    "cfg5": dict(B=131072, N=2048, n=8, L=4, w_var=1 / 8, dtype="bf16", act="tanh", seed=4, layers=12,
+                 desc="12 residual NCN layers D=2048 g=8 4 stages bf16, 131072 rows per GPU (1/8 of the 8-GPU global batch)"),
     "small": dict(B=8192, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="tanh", seed=1,
                   desc="cfg2 with 8192 rows (profiling case)"),
 }
@@ -182,8 +184,13 @@ def run_b200(args, wl, rank, world, local_rank):
     dy = torch.randn(B, N, 1, generator=g, device=dev, dtype=torch.float32).to(dtype)
     dya = torch.zeros(B, N, 1, device=dev, dtype=dtype)
     gw = torch.Generator().manual_seed(wl["seed"])
-    ws = [(torch.randn(2, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]
-    net = ncn.NCNNetTestCuda(0.9, wl["act"], n, 1, L, ws, backward_mode=mode)
+    layers = wl.get("layers", 0)
+    if layers:
+        net = ncn.NCNResidualStack(layers, 0.9, wl["act"], n, 1, L, 1, w_std=wl["w_var"] ** 0.5).to(dev)
+        ws = [net.weight]
+    else:
+        ws = [(torch.randn(2, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]
+        net = ncn.NCNNetTestCuda(0.9, wl["act"], n, 1, L, ws, backward_mode=mode)
 
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
 
@@ -233,7 +240,7 @@ def run_b200(args, wl, rank, world, local_rank):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = 6650.0, "fallback"
-    elems = B * N
+    elems = B * N * max(1, layers)  # every layer of a stack moves the same bytes
     bwd_bytes = 6 * w * elems  # reads y, ya, dy, dya; writes dx, dxa
     bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
     step_gbs = 10 * w * elems / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
@@ -253,15 +260,15 @@ def run_b200(args, wl, rank, world, local_rank):
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": {"workload": wl["desc"], "rows_per_gpu": B, "D": N, "g": n, "stages": L, "activation": wl["act"],
                    "backward_mode": mode, "parallelism": f"dp{world}", "l2": "inputs larger than L2 (>= 1 GB per tensor)"},
-        "roofline": roofline, "gpu_launches": 3 * args.steps, "clocks": clocks.summary(),
+        "roofline": roofline, "gpu_launches": 3 * args.steps * max(1, layers), "clocks": clocks.summary(),
         "rows_per_s_per_gpu": value / world,
     }
 
-    if rank == 0 and not args.no_e2e:
+    if rank == 0 and not args.no_e2e and not layers:
         line["e2e"] = run_e2e(ncn, wl, dev, dtype, ws, mode, world)
     if world > 1:
         dist.barrier()
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and not layers:
         v, threads, rows, dt = cpu_rows_per_s(wl, args.cpu_seconds)
         line["cpu_baseline"] = {
             "value": v, "unit": "rows/s", "cores": threads, "kind": "port",

@@ -74,9 +74,12 @@ def test_fp32_full_size(ncn, name, B, N, n, L, var, seed, every):
         part = _run(ncn, x[k * q:(k + 1) * q], xa[k * q:(k + 1) * q], dy[k * q:(k + 1) * q], dya[k * q:(k + 1) * q], W, n, every)
         acc += part[4]
     assert O.rel_err(acc, dW) < 1e-5
-    # and bitwise reproducible
+    # and bitwise reproducible for equal arguments (asking for the rebuilt input changes the launch
+    # plan and with it the summation order of dW, so compare two runs without it)
     again = _run(ncn, x, xa, dy, dya, W, n, every)
-    assert torch.equal(again[4], dW) and torch.equal(again[2], dx)
+    again2 = _run(ncn, x, xa, dy, dya, W, n, every)
+    assert torch.equal(again[4], again2[4]) and torch.equal(again[2], again2[2])
+    assert torch.equal(again[2], dx) and O.rel_err(again[4], dW) < 1e-6
 
 
 def test_bf16_beyond_2_31_elements(ncn):

@@ -60,7 +60,7 @@ def test_noalloc_rejects_what_exceeds_its_array():
 
     lib = _lib.load()
     dev = torch.device("cuda")
-    B, N, n, L = 65536, 64, 4, 40  # ~300 CTAs x 2L = 80 partial sums > 16384 floats
+    B, N, n, L = 65536, 64, 4, 60  # >= 148 CTAs x 2L = 120 partial sums > 16384 floats
     x = torch.randn(B, N, 1, device=dev)
     W = (torch.randn(L, 2, device=dev) * 0.1).contiguous()
     dx, dxa = torch.empty_like(x), torch.empty_like(x)
