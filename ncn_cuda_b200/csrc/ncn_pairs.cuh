@@ -250,8 +250,10 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_fwd_kernel(const RowsParams p
     const T* sa = sx + RN;
     float2* ck_tile = ckpt + row0 * N + base;
 
+    StageRec rec_next = recs[0];
     for (int l = 0; l < L; ++l) {
-      const StageRec rec = recs[l];
+      const StageRec rec = rec_next;
+      if (l + 1 < L) rec_next = recs[l + 1];  // in flight during this stage's work
       const int s = rec.s;
       const bool first = (l == 0), last = (l == L - 1);
       if (active) {
