@@ -43,7 +43,7 @@ WORKLOADS = {
 
 # DRAM bytes per element moved by the backward kernel in one launch, from the ncu capture
 # summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over B*N); None until measured.
-BWD_TRAFFIC_BYTES_PER_ELEMENT = 31.75  # profiles/pair_kernels_cfg2_small_ncu_full.md: 1065.2 MB over 33.55 M elements
+BWD_TRAFFIC_BYTES_PER_ELEMENT = 31.27  # profiles/pair_kernels_cfg2_small_ncu_full.md: 1049.2 MB over 33.55 M elements
 
 
 def parse():
@@ -245,9 +245,10 @@ def run_b200(args, wl, rank, world, local_rank):
     bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
     step_gbs = 10 * w * elems / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "pair_bwd_kernel (ncn_pairs.cuh)", "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
+        "bound": "hbm", "kernel": "pair_bwd_wide_kernel (ncn_pairs.cuh)", "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
         "unit": "GB/s", "frac": bwd_gbs / peak, "ms_per_launch": bwd_ms,
-        "traffic": (BWD_TRAFFIC_BYTES_PER_ELEMENT * elems if BWD_TRAFFIC_BYTES_PER_ELEMENT else None),
+        # measured on the cfg2 shape (fp32, one checkpoint); traffic grows in proportion to the rows
+        "traffic": (BWD_TRAFFIC_BYTES_PER_ELEMENT * elems if args.workload in ("cfg2", "small") and mode == "auto" else None),
         "algorithmic_bytes": bwd_bytes,
         "fwd_plus_bwd": {"achieved": step_gbs, "frac": step_gbs / peak, "frac_of_8TBs_nominal": step_gbs / 8000.0,
                          "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "algorithmic_bytes": 10 * w * elems},
