@@ -286,7 +286,7 @@ def run_e2e(ncn, wl, dev, dtype, ws, mode, world):
     pinned host memory, all copies inside the timed region (rank 0's GPU; the other ranks idle)."""
     from ncn_cuda_b200.host import net_fwd_bwd_host
 
-    B, N = min(wl["B"], 32768), wl["N"]
+    B, N = wl["B"], wl["N"]
     g = torch.Generator().manual_seed(wl["seed"])
     hx = torch.empty(B, N, 1, dtype=dtype).pin_memory()
     hx.copy_(torch.randn(B, N, 1, generator=g).to(dtype))
@@ -296,7 +296,7 @@ def run_e2e(ncn, wl, dev, dtype, ws, mode, world):
     hdya = torch.zeros(B, N, 1, dtype=dtype).pin_memory()
     out = tuple(torch.empty(B, N, 1, dtype=dtype).pin_memory() for _ in range(4))
     W = torch.stack([p.detach() for p in ws])
-    reps = 3
+    reps = 2
     net_fwd_bwd_host(hx, hxa, W, hdy, hdya, 0.9, wl["act"], wl["n"], 1, out=out, backward_mode=mode, device=dev)
     torch.cuda.synchronize()
     t0 = time.perf_counter()

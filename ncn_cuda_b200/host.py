@@ -19,7 +19,7 @@ from .ncn_pytorch_wrapper_v2 import plan_backward
 def net_fwd_bwd_host(
     x: torch.Tensor, xa: torch.Tensor, W: torch.Tensor, dy: torch.Tensor, dya: torch.Tensor,
     alpha: float, activation, n_cache: int, n_head: int,
-    out: Optional[Tuple[torch.Tensor, ...]] = None, chunk_rows: int = 8192, backward_mode: str = "auto",
+    out: Optional[Tuple[torch.Tensor, ...]] = None, chunk_rows: int = 4096, backward_mode: str = "auto",
     device: Optional[torch.device] = None,
 ):
     """x, xa, dy, dya: CPU tensors [B, N, E] (pinned for full copy bandwidth); W: [L, 2E].
