@@ -284,3 +284,23 @@ def test_error_behaviour(ncn):
         ncn.ops.net_fwd(x, x, W.reshape(1, 8), 0.9, 0, 5, 1)  # E != 1: fused path does not apply
     assert e.value.status == 5
     ncn.ops.device_status()
+
+
+# ---------------------------------------------------------------- host-buffer entry (the e2e path of bench.py)
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL32), (torch.bfloat16, TOLBF)])
+def test_host_buffer_pipeline(ncn, dtype, tol):
+    from ncn_cuda_b200.host import net_fwd_bwd_host
+
+    B, N, n, L = 100, 512, 4, 6  # 100 rows in chunks of 16: ragged last chunk, dW accumulated over 7 chunks
+    x, xa, ws, dy, dya = O.make_inputs(21, B, N, 1, L, 0.25, dya_zero=False)
+    x, dy, dya = (t.to(dtype).float() for t in (x, dy, dya))
+    want = O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, "tanh", n, 1)
+    host = [t.to(dtype).pin_memory() for t in (x, xa, dy, dya)]
+    W = torch.stack(ws)
+    y, ya, dx, dxa, dW = net_fwd_bwd_host(host[0], host[1], W, host[2], host[3], 0.9, "tanh", n, 1, chunk_rows=16)
+    ncn.ops.device_status()
+    assert not y.is_cuda and not dW.is_cuda
+    assert_close((y, ya, dx, dxa, [dW[l] for l in range(L)]), want, tol)
+    # same call again: bitwise identical (fixed chunk order)
+    y2, ya2, dx2, dxa2, dW2 = net_fwd_bwd_host(host[0], host[1], W, host[2], host[3], 0.9, "tanh", n, 1, chunk_rows=16)
+    assert torch.equal(dW, dW2) and torch.equal(dx, dx2)
