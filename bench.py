@@ -33,9 +33,9 @@ WORKLOADS = {
                         desc="as cfg2 with linear activation"),
     "cfg4": dict(B=131072, N=4096, n=8, L=4, w_var=0.01, dtype="f32", act="tanh", seed=3, mode="invert",
                  desc="invertible variant fp32 x[131072,4096] g=8 4 stages"),
-    "cfg3": dict(B=262144, N=8192, n=16, L=4, w_var=1 / 16, dtype="bf16", act="tanh", seed=2,
+    "cfg3": dict(B=262144, N=8192, n=16, L=4, w_var=1 / 16, dtype="bf16", act="tanh", seed=2, mode="tape",
                  desc="bf16 storage x[262144,8192] g=16 4 stages"),
-    "cfg5": dict(B=131072, N=2048, n=8, L=4, w_var=1 / 8, dtype="bf16", act="tanh", seed=4, layers=12,
+    "cfg5": dict(B=131072, N=2048, n=8, L=4, w_var=1 / 8, dtype="bf16", act="tanh", seed=4, layers=12, mode="tape",
                  desc="12 residual NCN layers D=2048 g=8 4 stages bf16, 131072 rows per GPU (1/8 of the 8-GPU global batch)"),
     "small": dict(B=8192, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="tanh", seed=1,
                   desc="cfg2 with 8192 rows (profiling case)"),
@@ -53,7 +53,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
-    ap.add_argument("--mode", default=None, help="backward mode override: auto|checkpoint|invert|recompute")
+    ap.add_argument("--mode", default=None, help="backward mode override: auto|checkpoint|invert|recompute|tape")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
@@ -186,7 +186,8 @@ def run_b200(args, wl, rank, world, local_rank):
     gw = torch.Generator().manual_seed(wl["seed"])
     layers = wl.get("layers", 0)
     if layers:
-        net = ncn.NCNResidualStack(layers, 0.9, wl["act"], n, 1, L, 1, w_std=wl["w_var"] ** 0.5).to(dev)
+        net = ncn.NCNResidualStack(layers, 0.9, wl["act"], n, 1, L, 1, w_std=wl["w_var"] ** 0.5,
+                                   backward_mode="recompute" if mode == "auto" else mode).to(dev)
         ws = [net.weight]
     else:
         ws = [(torch.randn(2, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]

@@ -51,8 +51,12 @@ enum {
 /* flags of the net calls */
 enum {
   NCN_RESIDUAL = 1,  /* forward: y = x + net(x, xa).x ; backward: dx = dx_net + dy */
-  NCN_RECOMPUTE = 2  /* backward: s0/s1 are the net INPUT (x, xa); the forward is replayed in fp32.
-                        Required with bf16 storage and with NCN_RESIDUAL. */
+  NCN_RECOMPUTE = 2, /* backward: s0/s1 are the net INPUT (x, xa); the forward is replayed in fp32.
+                        With bf16 storage or NCN_RESIDUAL use this or NCN_TAPE. */
+  NCN_TAPE = 8       /* forward: also keep the fp32 state after the LAST stage (before the residual add) in
+                        ckpt, one slot after the periodic ones.  backward (same flag, same ckpt, same
+                        ckpt_every): starts from that state, s0/s1 are not read and may be null.  The
+                        alternative to NCN_RECOMPUTE: no forward replay, 8 more bytes per element kept. */
 };
 
 /* One stage forward.  Replaces ncn_cuda_module.forward (ncn_cuda/ncn_cuda.cpp:30;
@@ -73,8 +77,9 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
 
 /* All L stages (module_l = first_module .. first_module+L-1) in one kernel.  Replaces the stage
  * loops NCNNetCuda.forward / NCNNetTestCuda.forward (ncn_pytorch_wrapper_v2.py:114-117,132-144).
- * ckpt (may be null): fp32 buffer of ncn_ckpt_bytes(...) bytes that receives the state after every
- * ckpt_every-th stage, for ncn_net_bwd.  Returns NCN_ERR_UNSUPPORTED where only the per-stage calls
+ * ckpt (may be null without NCN_TAPE): fp32 buffer of ncn_ckpt_bytes(...) bytes that receives the state
+ * after every ckpt_every-th stage (ckpt_every <= 0: none) and, with NCN_TAPE, after the last one, for
+ * ncn_net_bwd.  Returns NCN_ERR_UNSUPPORTED where only the per-stage calls
  * apply (E != 1, n_cache not in {2,4,8,16}, N not a multiple of 4 (fp32) / 8 (bf16)). */
 int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya, float* ckpt, int ckpt_every,
                 int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module, int L, double alpha,
@@ -82,7 +87,7 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
 
 /* Backward of ncn_net_fwd in one kernel.  s0/s1 are the net OUTPUT (y, ya) — every stage input is
  * rebuilt by the reversible inverse, restarting at each stored checkpoint — or, with NCN_RECOMPUTE,
- * the net INPUT.  dW is [L][2E] fp32; with dw_accumulate != 0 the result is added to it.
+ * the net INPUT, or unused with NCN_TAPE.  dW is [L][2E] fp32; with dw_accumulate != 0 the result is added to it.
  * x_rec / xa_rec may be null. */
 int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
                 void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, void* workspace,
@@ -111,15 +116,18 @@ int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* dy, const vo
                         int64_t N, int64_t E, int n_cache, int n_head, int first_module, int L, double alpha,
                         int activation, int dtype, int flags, int dw_accumulate, void* stream);
 
-/* 1 if ncn_net_fwd / ncn_net_bwd cover these arguments on the current device, else 0. */
+/* 1 if ncn_net_fwd / ncn_net_bwd (without x_rec / xa_rec, whose staging needs more shared memory and
+ * may still return NCN_ERR_SMEM for the longest rows) cover these arguments on the current device,
+ * else 0.  flags and ckpt_every as they will be passed to the net calls. */
 int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype, int flags,
                       int ckpt_every);
 
 /* Workspace (bytes) that ncn_stage_bwd (L = 1) or ncn_net_bwd needs for these arguments. */
 size_t ncn_bwd_workspace_bytes(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype);
 
-/* Size (bytes) of the checkpoint buffer: ((L-1)/ckpt_every) states of 2 x [B, N, E] fp32. */
-size_t ncn_ckpt_bytes(int64_t B, int64_t N, int64_t E, int L, int ckpt_every);
+/* Size (bytes) of the checkpoint buffer: (L-1)/ckpt_every states (0 for ckpt_every <= 0), one more
+ * with NCN_TAPE in flags, each 2 x [B, N, E] fp32. */
+size_t ncn_ckpt_bytes(int64_t B, int64_t N, int64_t E, int L, int ckpt_every, int flags);
 
 /* Reads and clears the device status word (synchronises the device): NCN_OK, or
  * NCN_ERR_DEVICE_WAIT if a kernel abandoned a bounded wait since the last call. */

@@ -13,7 +13,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libncn_b200.so")
 
 NCN_F32, NCN_BF16 = 0, 1
-NCN_RESIDUAL, NCN_RECOMPUTE = 1, 2
+NCN_RESIDUAL, NCN_RECOMPUTE, NCN_TAPE = 1, 2, 8
 NCN_OK, NCN_ERR_SMEM, NCN_ERR_UNSUPPORTED = 0, 4, 5
 
 # name -> (restype, argtypes); must list every function of include/ncn_b200.h
@@ -41,7 +41,7 @@ SIGNATURES = {
     ),
     "ncn_net_supported": (c_int, [c_int64] * 3 + [c_int] * 6),
     "ncn_bwd_workspace_bytes": (c_size_t, [c_int64] * 3 + [c_int] * 4),
-    "ncn_ckpt_bytes": (c_size_t, [c_int64] * 3 + [c_int] * 2),
+    "ncn_ckpt_bytes": (c_size_t, [c_int64] * 3 + [c_int] * 3),
     "ncn_device_status": (c_int, []),
     "ncn_status_string": (c_char_p, [c_int]),
     "ncn_last_cuda_error": (c_char_p, []),

@@ -131,6 +131,7 @@ static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, i
   pl.pair = pair_fn(n, bwd) != nullptr && m % 2 == 0 && m / 2 <= pair_max_threads(n, bwd) && !(nopair && nopair[0] == '1');
   const bool wide = bwd && pl.pair && want_wide;
   if (wide) pl.variant = 1;  // separate buffers: planned by the general layout below
+  if (pl.pair && bwd && !wide && (flags & F_TAPE)) pl.pair = false;  // the aliased variant has no tape path
   if (pl.pair && bwd && !wide) {
     // pair backward: one 16-byte slot per position doubles as TMA landing zone and output staging
     const bool residual = (flags & F_RESIDUAL) != 0;
@@ -392,9 +393,14 @@ size_t ncn_bwd_workspace_bytes(int64_t B, int64_t N, int64_t E, int n_cache, int
   return workspace_floats(dev, E, L) * sizeof(float);
 }
 
-size_t ncn_ckpt_bytes(int64_t B, int64_t N, int64_t E, int L, int ckpt_every) {
-  if (ckpt_every <= 0 || L <= 1) return 0;
-  return (size_t)((L - 1) / ckpt_every) * 2 * (size_t)B * (size_t)N * (size_t)E * sizeof(float);
+// stored states: one after every ckpt_every-th stage except the last, plus the last one with F_TAPE
+static int ckpt_slots(int L, int ckpt_every, int flags) {
+  if (L < 1) return 0;
+  return (ckpt_every > 0 ? (L - 1) / ckpt_every : 0) + ((flags & F_TAPE) ? 1 : 0);
+}
+
+size_t ncn_ckpt_bytes(int64_t B, int64_t N, int64_t E, int L, int ckpt_every, int flags) {
+  return (size_t)ckpt_slots(L, ckpt_every, flags) * 2 * (size_t)B * (size_t)N * (size_t)E * sizeof(float);
 }
 
 int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int L, int dtype, int flags,
@@ -404,9 +410,10 @@ int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, 
   DevInfo dev;
   if (get_dev(dev) != NCN_OK) return 0;
   Plan pl;
-  const int n_ck = ckpt_every > 0 ? (L - 1) / ckpt_every : 0;
+  if ((flags & F_TAPE) && (flags & F_RECOMPUTE)) return 0;
+  const int n_ck = (flags & F_RECOMPUTE) ? 0 : ckpt_slots(L, ckpt_every, flags);
   if (plan_rows(false, B, (int)N, n_cache, L, dtype, flags, 0, false, dev, ACT_TANH, pl) != NCN_OK) return 0;
-  if (plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, true, dev, ACT_TANH, pl) != NCN_OK) return 0;
+  if (plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, false, dev, ACT_TANH, pl) != NCN_OK) return 0;
   return 1;
 }
 
@@ -417,6 +424,7 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
   if (rc != NCN_OK) return rc;
   if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
   if (!x || !xa || !W || !y || !ya) return NCN_ERR_NULL;
+  if ((flags & F_TAPE) && !ckpt) return NCN_ERR_NULL;
   if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(xa) || !aligned16(y) || !aligned16(ya) || (ckpt && !aligned16(ckpt)))
     return NCN_ERR_ALIGN;
@@ -428,12 +436,12 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
   RowsParams p{};
   p.in[0] = x; p.in[1] = xa;
   p.out[0] = y; p.out[1] = ya;
-  p.ckpt = (ckpt && ckpt_every > 0 && (L - 1) / ckpt_every > 0) ? ckpt : nullptr;
+  p.ckpt = (ckpt && ckpt_slots(L, ckpt_every, flags) > 0) ? ckpt : nullptr;
   p.ckpt_every = ckpt_every;
   p.W = W;
   p.status = dev.status;
   p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
-  p.flags = flags & F_RESIDUAL;
+  p.flags = flags & (F_RESIDUAL | F_TAPE);
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);
@@ -449,10 +457,12 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
   int rc = check_common(B, N, E, n_cache, n_head, dtype);
   if (rc != NCN_OK) return rc;
   if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
-  if (!s0 || !s1 || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  const bool tape = (flags & F_TAPE) != 0;  // the state after the last stage comes from ckpt; s0, s1 unused
+  if (tape && (flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
+  if ((!tape && (!s0 || !s1)) || (tape && !ckpt) || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
   if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
   if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
-  if ((flags & F_RESIDUAL) && !(flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
+  if ((flags & F_RESIDUAL) && !(flags & (F_RECOMPUTE | F_TAPE))) return NCN_ERR_UNSUPPORTED;
   if (!aligned16(s0) || !aligned16(s1) || !aligned16(dy) || !aligned16(dya) || !aligned16(dx) || !aligned16(dxa) ||
       (x_rec && (!aligned16(x_rec) || !aligned16(xa_rec))) || (ckpt && !aligned16(ckpt)))
     return NCN_ERR_ALIGN;
@@ -460,8 +470,8 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
   if (!workspace || workspace_bytes < workspace_floats(dev, E, L) * sizeof(float)) return NCN_ERR_WORKSPACE;
   const int act = fused_act(map_act(activation), dtype);
-  const bool use_ck = ckpt && ckpt_every > 0 && !(flags & F_RECOMPUTE) && (L - 1) / ckpt_every > 0;
-  const int n_ck = use_ck ? (L - 1) / ckpt_every : 0;
+  const bool use_ck = ckpt && !(flags & F_RECOMPUTE) && ckpt_slots(L, ckpt_every, flags) > 0;
+  const int n_ck = use_ck ? ckpt_slots(L, ckpt_every, flags) : 0;
   Plan pl;
   if ((rc = plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, x_rec != nullptr, dev, act, pl)) != NCN_OK)
     return rc;
@@ -474,7 +484,7 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
   p.partials = static_cast<float*>(workspace);
   p.status = dev.status;
   p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
-  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE)) | (pl.red_thread ? F_RED_THREAD : 0);
+  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE | F_TAPE)) | (pl.red_thread ? F_RED_THREAD : 0);
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);
@@ -603,10 +613,12 @@ extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* d
   int rc = check_common(B, N, E, n_cache, n_head, dtype);
   if (rc != NCN_OK) return rc;
   if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
-  if (!s0 || !s1 || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  const bool tape = (flags & F_TAPE) != 0;  // the state after the last stage comes from ckpt; s0, s1 unused
+  if (tape && (flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
+  if ((!tape && (!s0 || !s1)) || (tape && !ckpt) || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
   if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
   if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
-  if ((flags & F_RESIDUAL) && !(flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
+  if ((flags & F_RESIDUAL) && !(flags & (F_RECOMPUTE | F_TAPE))) return NCN_ERR_UNSUPPORTED;
   if (!aligned16(s0) || !aligned16(s1) || !aligned16(dy) || !aligned16(dya) || !aligned16(dx) || !aligned16(dxa) ||
       (x_rec && (!aligned16(x_rec) || !aligned16(xa_rec))) || (ckpt && !aligned16(ckpt)))
     return NCN_ERR_ALIGN;
@@ -615,8 +627,8 @@ extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* d
   float* scratch = nullptr;
   if ((rc = noalloc_scratch(&scratch)) != NCN_OK) return rc;
   const int act = fused_act(map_act(activation), dtype);
-  const bool use_ck = ckpt && ckpt_every > 0 && !(flags & F_RECOMPUTE) && (L - 1) / ckpt_every > 0;
-  const int n_ck = use_ck ? (L - 1) / ckpt_every : 0;
+  const bool use_ck = ckpt && !(flags & F_RECOMPUTE) && ckpt_slots(L, ckpt_every, flags) > 0;
+  const int n_ck = use_ck ? ckpt_slots(L, ckpt_every, flags) : 0;
   Plan pl;
   if ((rc = plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, x_rec != nullptr, dev, act, pl)) != NCN_OK)
     return rc;
@@ -631,7 +643,7 @@ extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* d
   p.partials = scratch;  // every element the reduction reads is written by the kernel first
   p.status = dev.status;
   p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
-  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE)) | (pl.red_thread ? F_RED_THREAD : 0);
+  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE | F_TAPE)) | (pl.red_thread ? F_RED_THREAD : 0);
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
   fill_offsets(p, pl);

@@ -28,6 +28,7 @@ enum : int {
   F_RESIDUAL = 1,   // forward: y = x + net(x); backward: dx = dx_net + dy
   F_RECOMPUTE = 2,  // backward: inputs are the net INPUT; replay the forward, then walk back
   F_RED_THREAD = 4, // backward (set by the launch plan): dW partial slots per thread instead of per warp
+  F_TAPE = 8,       // the state after the LAST stage is checkpointed too (fp32); the backward starts from it
 };
 
 // error codes stored in the device status word by a kernel that gave up a wait

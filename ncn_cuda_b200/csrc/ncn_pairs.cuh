@@ -275,6 +275,14 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_fwd_kernel(const RowsParams p
           }
         }
         pair_forward<NG, ACT>(X, A, w);
+        if (rec.ck >= 0) {  // filed under this stage's groups: the backward of this stage reads o*m + g
+          float2* ck = ck_tile + (long long)rec.ck * BN + t;
+#pragma unroll
+          for (int o = 0; o < NG; ++o) {
+            ck[o * m] = make_float2(X[o].x, A[o].x);
+            ck[o * m + mh] = make_float2(X[o].y, A[o].y);
+          }
+        }
         if (last) {
           if (residual) {
             float2 xin[NG];
@@ -290,14 +298,6 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_fwd_kernel(const RowsParams p
           for (int o = 0; o < NG; ++o) {
             sts64(aa[o], X[o].x, A[o].x);
             sts64(ab[o], X[o].y, A[o].y);
-          }
-          if (rec.ck >= 0) {  // filed under this stage's groups: the backward of this stage reads o*m + g
-            float2* ck = ck_tile + (long long)rec.ck * BN + t;
-#pragma unroll
-            for (int o = 0; o < NG; ++o) {
-              ck[o * m] = make_float2(X[o].x, A[o].x);
-              ck[o * m + mh] = make_float2(X[o].y, A[o].y);
-            }
           }
         }
       }
@@ -584,6 +584,9 @@ __global__ void __launch_bounds__(MAXT, 1) pair_bwd_wide_kernel(const RowsParams
   const bool want_rec = p.out[2] != nullptr;
   const long long BN = p.B * (long long)N;
   const bool ck_smem = p.n_ckpt_slots > 0;
+  const bool tape = (p.flags & F_TAPE) != 0 && !recompute;
+  // the staged checkpoints are free again after the stage that uses the earliest one
+  const int ck_free_stage = (p.ckpt_every > 0 && (L - 1) / p.ckpt_every > 0) ? p.ckpt_every - 1 : L - 1;
 
   if (tid == 0) {
     mbar_init(&bar[0], 1);
@@ -603,9 +606,10 @@ __global__ void __launch_bounds__(MAXT, 1) pair_bwd_wide_kernel(const RowsParams
     const long long row0 = tl * R;
     const int rows = (int)min((long long)R, p.B - row0);
     const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
-    mbar_expect_tx(&bar[0], 4 * bytes);
+    mbar_expect_tx(&bar[0], (tape ? 2 : 4) * bytes);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) bulk_g2s(in_s + q * RN, g_in[q] + row0 * N, bytes, &bar[0]);
+    for (int q = 0; q < 4; ++q)
+      if (q >= 2 || !tape) bulk_g2s(in_s + q * RN, g_in[q] + row0 * N, bytes, &bar[0]);  // tape: no y, ya
   };
   auto issue_ckpt = [&](long long tl) {
     const long long row0 = tl * R;
@@ -698,7 +702,9 @@ __global__ void __launch_bounds__(MAXT, 1) pair_bwd_wide_kernel(const RowsParams
         if (first) {
           ld_native_pair<NG, T>(s0 + 2 * RN, t, s, m, H);
           ld_native_pair<NG, T>(s0 + 3 * RN, t, s, m, G);
-          if (!recompute) {
+          if (tape) {
+            // the state after the last stage comes from its checkpoint below
+          } else if (!recompute) {
             ld_native_pair<NG, T>(s0, t, s, m, X);
             ld_native_pair<NG, T>(s0 + RN, t, s, m, A);
           } else {
@@ -718,6 +724,8 @@ __global__ void __launch_bounds__(MAXT, 1) pair_bwd_wide_kernel(const RowsParams
             H[o] = make_float2(va.z, vb.z);
             G[o] = make_float2(va.w, vb.w);
           }
+        }
+        {
           if (rec.ck >= 0) {
             if ((uint32_t)rec.ck < p.n_ckpt_slots) {
               const float2* c = sck + rec.ck * RN + base + t;
@@ -780,7 +788,7 @@ __global__ void __launch_bounds__(MAXT, 1) pair_bwd_wide_kernel(const RowsParams
       if (last) fence_proxy_async();
       __syncthreads();
       if (tid == 0 && next < p.tiles && (residual ? last : first)) issue_load(next);
-      if (ck_smem && tid == 0 && next < p.tiles && l == p.ckpt_every - 1) issue_ckpt(next);
+      if (ck_smem && tid == 0 && next < p.tiles && l == ck_free_stage) issue_ckpt(next);
     }
     if (tid == 0) {
       const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));

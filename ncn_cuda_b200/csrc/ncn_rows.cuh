@@ -95,7 +95,7 @@ __device__ __forceinline__ void group_addrs(uint32_t row_addr, int g, int s, int
 
 // Stage table: scaled weights, stride s = 0 for stage 0 else 2^(stage-1) mod m
 // (torch_ref/ncn_pytorch.py:38), and the checkpoint index (a state is kept after every
-// ckpt_every-th stage except the last).
+// ckpt_every-th stage except the last; with F_TAPE the last stage's state takes the slot after those).
 __device__ __forceinline__ void fill_stage_table(StageRec* rec, const RowsParams& p, bool have_ckpt, int tid, int nthr) {
   for (int i = tid; i < p.L; i += nthr) {
     StageRec r;
@@ -103,6 +103,7 @@ __device__ __forceinline__ void fill_stage_table(StageRec* rec, const RowsParams
     r.owj = p.W[2 * i + 1] * p.oma;
     r.s = stage_stride(p.l0 + i, p.m);
     r.ck = (have_ckpt && p.ckpt_every > 0 && i != p.L - 1 && ((i + 1) % p.ckpt_every == 0)) ? (i + 1) / p.ckpt_every - 1 : -1;
+    if (have_ckpt && (p.flags & F_TAPE) && i == p.L - 1) r.ck = p.ckpt_every > 0 ? (p.L - 1) / p.ckpt_every : 0;
     rec[i] = r;
   }
 }
@@ -194,6 +195,11 @@ __global__ void __launch_bounds__(MAXT, 1) rows_fwd_kernel(const RowsParams p) {
           }
         }
         group_forward<NG, ACT>(x, a, w);
+        if (rec.ck >= 0) {  // filed under this stage's groups: the backward of this stage reads o*m + g
+          float2* ck = ck_tile + (long long)rec.ck * BN + base + g;
+#pragma unroll
+          for (int o = 0; o < NG; ++o) ck[o * m] = make_float2(x[o], a[o]);
+        }
         if (last) {
           if (residual) {
             float xin[NG];
@@ -207,11 +213,6 @@ __global__ void __launch_bounds__(MAXT, 1) rows_fwd_kernel(const RowsParams p) {
           if (first) group_addrs<NG, 3>(work_addr + ((uint32_t)base << 3), g, s, m, adr);
 #pragma unroll
           for (int o = 0; o < NG; ++o) sts64(adr[o], x[o], a[o]);
-          if (rec.ck >= 0) {  // filed under this stage's groups: the backward of this stage reads o*m + g
-            float2* ck = ck_tile + (long long)rec.ck * BN + base + g;
-#pragma unroll
-            for (int o = 0; o < NG; ++o) ck[o * m] = make_float2(x[o], a[o]);
-          }
         }
         r += dr; g += dg;
         if (g >= m) { g -= m; ++r; }
@@ -274,7 +275,10 @@ __global__ void __launch_bounds__(MAXT, 1) rows_bwd_kernel(const RowsParams p) {
   const bool residual = (p.flags & F_RESIDUAL) != 0;
   const bool recompute = (p.flags & F_RECOMPUTE) != 0;
   const bool want_rec = p.out[2] != nullptr;
+  const bool tape = (p.flags & F_TAPE) != 0 && !recompute;
   const long long BN = p.B * (long long)N;
+  // the staged checkpoints are free again after the stage that uses the earliest one
+  const int ck_free_stage = (p.ckpt_every > 0 && (L - 1) / p.ckpt_every > 0) ? p.ckpt_every - 1 : L - 1;
 
   if (tid == 0) {
     mbar_init(&bar[0], 1);
@@ -290,9 +294,10 @@ __global__ void __launch_bounds__(MAXT, 1) rows_bwd_kernel(const RowsParams p) {
     const long long row0 = t * R;
     const int rows = (int)min((long long)R, p.B - row0);
     const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
-    mbar_expect_tx(&bar[b], 4 * bytes);
+    mbar_expect_tx(&bar[b], (tape ? 2 : 4) * bytes);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) bulk_g2s(in_s[b] + q * RN, g_in[q] + row0 * N, bytes, &bar[b]);
+    for (int q = 0; q < 4; ++q)
+      if (q >= 2 || !tape) bulk_g2s(in_s[b] + q * RN, g_in[q] + row0 * N, bytes, &bar[b]);  // tape: no y, ya
   };
   // Checkpoints staged in shared memory (only with a single in buffer, so bar[1] is free for
   // them): all of a tile's checkpoints arrive together and stay until the stage that uses the
@@ -390,7 +395,9 @@ __global__ void __launch_bounds__(MAXT, 1) rows_bwd_kernel(const RowsParams p) {
         if (first) {
           ld_native<NG, T>(sgy + base, g, s, m, gx);
           ld_native<NG, T>(sga + base, g, s, m, ga);
-          if (!recompute) {
+          if (use_ck) {
+            // tape: filled below from the checkpoint
+          } else if (!recompute) {
             ld_native<NG, T>(s0 + base, g, s, m, x);
             ld_native<NG, T>(s1 + base, g, s, m, a);
           } else {
@@ -406,6 +413,8 @@ __global__ void __launch_bounds__(MAXT, 1) rows_bwd_kernel(const RowsParams p) {
             const float4 v = lds128(adr[o]);
             x[o] = v.x; a[o] = v.y; gx[o] = v.z; ga[o] = v.w;
           }
+        }
+        {
           if (use_ck) {
             if ((uint32_t)rec.ck < p.n_ckpt_slots) {
               const float2* c = sck + rec.ck * RN + base + g;
@@ -463,7 +472,7 @@ __global__ void __launch_bounds__(MAXT, 1) rows_bwd_kernel(const RowsParams p) {
       if (last) fence_proxy_async();
       __syncthreads();
       if (p.nbuf == 1 && tid == 0 && next < p.tiles && (residual ? last : first)) issue_load(next, 0);
-      if (ck_smem && tid == 0 && next < p.tiles && l == p.ckpt_every - 1) issue_ckpt(next);
+      if (ck_smem && tid == 0 && next < p.tiles && l == ck_free_stage) issue_ckpt(next);
     }
     if (tid == 0) {
       const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));

@@ -32,7 +32,7 @@ def net_fwd_bwd_host(
     y_h, ya_h, dx_h, dxa_h = out
     Wd = W.to(device=device, dtype=torch.float32).contiguous()
     dW = torch.zeros(L, W.shape[1], dtype=torch.float32, device=device)
-    recompute, every = plan_backward(x.dtype, n_cache, L, False, backward_mode)
+    recompute, every, tape = plan_backward(x.dtype, n_cache, L, False, backward_mode)
     act = ops.activation_code(activation)
 
     main = torch.cuda.current_stream(device)
@@ -59,8 +59,11 @@ def net_fwd_bwd_host(
             ev_in.record(s_in)
         with torch.cuda.stream(s_k):
             s_k.wait_event(ev_in)
-            y, ya, ckpt = ops.net_fwd(bufs[0], bufs[1], Wd, alpha, act, n_cache, n_head, 0, every, False)
-            if recompute:
+            y, ya, ckpt = ops.net_fwd(bufs[0], bufs[1], Wd, alpha, act, n_cache, n_head, 0, every, False, tape)
+            if tape:
+                res = ops.net_bwd(None, None, bufs[2], bufs[3], Wd, alpha, act, n_cache, n_head, 0, ckpt=ckpt,
+                                  ckpt_every=every, dW_out=dW, tape=True)
+            elif recompute:
                 res = ops.net_bwd(bufs[0], bufs[1], bufs[2], bufs[3], Wd, alpha, act, n_cache, n_head, 0,
                                   recompute=True, dW_out=dW)
             else:

@@ -68,27 +68,35 @@ def fused_ncn_cuda_v2(
 
 
 def plan_backward(dtype, n_cache: int, num_modules: int, residual: bool, backward_mode: str):
-    """-> (recompute, ckpt_every) for a fused net.
+    """-> (recompute, ckpt_every, tape) for a fused net.
 
     "invert"      rebuild everything from the net output (the reference's reversible backward
                   applied across all stages; nothing but the output is stored)
     "checkpoint"  as invert, but the forward also stores the state every few stages so that no
                   inverse chain exceeds MAX_INVERSE_STEPS steps
     "recompute"   store the net input and replay the forward in fp32 inside the backward kernel
+    "tape"        as checkpoint, and the fp32 state after the last stage is stored too: the backward
+                  starts from it and reads neither the net input nor its output.  The faster choice
+                  for bf16 storage and residual layers (no replay) at 8 more bytes per element;
+                  with bf16 storage the periodic states are four times sparser
     "auto"        recompute for bf16 storage and residual layers, else checkpoint
     """
-    if backward_mode not in ("auto", "invert", "checkpoint", "recompute"):
+    if backward_mode not in ("auto", "invert", "checkpoint", "recompute", "tape"):
         raise ValueError(f"unknown backward_mode {backward_mode!r}")
     if backward_mode == "auto":
         backward_mode = "recompute" if (dtype != torch.float32 or residual) else "checkpoint"
-    if residual and backward_mode != "recompute":
-        raise ValueError("residual layers need backward_mode='recompute'")
+    if residual and backward_mode not in ("recompute", "tape"):
+        raise ValueError("residual layers need backward_mode='recompute' or 'tape'")
     if backward_mode == "recompute":
-        return True, 0
+        return True, 0, False
     if backward_mode == "invert":
-        return False, 0
-    every = max(1, MAX_INVERSE_STEPS // n_cache)
-    return False, (every if num_modules > every else 0)
+        return False, 0, False
+    tape = backward_mode == "tape"
+    # With bf16 storage the results are rounded to 2^-9 anyway: a four times longer inverse chain
+    # (rounding grows to about 1e-4 relative over 64 steps) stays far below that.
+    budget = MAX_INVERSE_STEPS * (4 if (tape and dtype != torch.float32) else 1)
+    every = max(1, budget // n_cache)
+    return False, (every if num_modules > every else 0), tape
 
 
 class NCNNetFunction(torch.autograd.Function):
@@ -96,23 +104,29 @@ class NCNNetFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, xa, W, alpha, activation, n_cache, n_head, first_module, backward_mode, residual):
-        recompute, every = plan_backward(x.dtype, n_cache, W.shape[0], residual, backward_mode)
-        y, ya, ckpt = ops.net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module, every, residual)
-        if recompute:
+        recompute, every, tape = plan_backward(x.dtype, n_cache, W.shape[0], residual, backward_mode)
+        y, ya, ckpt = ops.net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module, every, residual, tape)
+        if tape:
+            ctx.save_for_backward(W)  # the stored states are all the backward reads
+        elif recompute:
             ctx.save_for_backward(x, xa, W)
         else:
             ctx.save_for_backward(y, ya, W)
         ctx.ckpt = ckpt
-        ctx.cfg = (alpha, activation, n_cache, n_head, first_module, every, recompute, residual)
+        ctx.cfg = (alpha, activation, n_cache, n_head, first_module, every, recompute, residual, tape)
         return y, ya
 
     @staticmethod
     def backward(ctx, dy, dya):
-        s0, s1, W = ctx.saved_tensors
-        alpha, activation, n_cache, n_head, first_module, every, recompute, residual = ctx.cfg
+        alpha, activation, n_cache, n_head, first_module, every, recompute, residual, tape = ctx.cfg
+        if tape:
+            (W,) = ctx.saved_tensors
+            s0 = s1 = None
+        else:
+            s0, s1, W = ctx.saved_tensors
         dx, dxa, dW = ops.net_bwd(
             s0, s1, dy, dya, W, alpha, activation, n_cache, n_head, first_module,
-            ckpt=ctx.ckpt, ckpt_every=every, recompute=recompute, residual=residual,
+            ckpt=ctx.ckpt, ckpt_every=every, recompute=recompute, residual=residual, tape=tape,
         )
         ctx.ckpt = None
         return dx, dxa, dW.to(W.dtype), None, None, None, None, None, None, None
@@ -126,7 +140,12 @@ def fused_ncn_net(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, 
 def _net_forward(x, xa, weights: Sequence[torch.Tensor], alpha, activation_nr, n_cache, n_head, backward_mode):
     """Shared by the two net modules: fused when the library covers the shape, else stage by stage."""
     L = len(weights)
-    if L > 0 and x.is_cuda and ops.net_supported(x, n_cache, n_head, L):
+    fused = False
+    if L > 0 and x.is_cuda:
+        recompute, every, tape = plan_backward(x.dtype, n_cache, L, False, backward_mode)
+        flags = (ops.NCN_RECOMPUTE if recompute else 0) | (ops.NCN_TAPE if tape else 0)
+        fused = ops.net_supported(x, n_cache, n_head, L, flags, every)
+    if fused:
         W = torch.stack([w.reshape(-1) for w in weights])
         return fused_ncn_net(x, xa, W, alpha, activation_nr, n_cache, n_head, 0, backward_mode)
     for module_nr in range(L):

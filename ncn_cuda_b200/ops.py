@@ -10,7 +10,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import NCN_BF16, NCN_F32, NCN_RECOMPUTE, NCN_RESIDUAL
+from ._lib import NCN_BF16, NCN_F32, NCN_RECOMPUTE, NCN_RESIDUAL, NCN_TAPE
 
 # activation vocabulary of the reference's CUDA wrapper (ncn_cuda/ncn_pytorch_wrapper_v2.py:111)
 ACTIVATION_CODES = {"tanh": 0, "relu": 1, "sigmoid": 2, "linear": -1}
@@ -115,8 +115,9 @@ def stage_bwd(y, ya, dy, dya, W, alpha, activation, n_cache, n_head, module_l, w
     return dx, dxa, dW
 
 
-def net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, ckpt_every=0, residual=False):
-    """All stages in one kernel.  W: [L, 2E].  Returns (y, ya, ckpt or None)."""
+def net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, ckpt_every=0, residual=False, tape=False):
+    """All stages in one kernel.  W: [L, 2E].  Returns (y, ya, ckpt or None).  ckpt holds the fp32
+    state after every ckpt_every-th stage and, with tape, after the last one."""
     lib = _lib.load()
     _check_inputs(x, xa)
     x, xa = x.contiguous(), xa.contiguous()
@@ -126,40 +127,49 @@ def net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, ckpt_e
     y, ya = torch.empty_like(x), torch.empty_like(xa)
     ckpt = None
     with torch.cuda.device(x.device):
-        nbytes = lib.ncn_ckpt_bytes(B, N, E, L, ckpt_every)
+        flags = (NCN_RESIDUAL if residual else 0) | (NCN_TAPE if tape else 0)
+        nbytes = lib.ncn_ckpt_bytes(B, N, E, L, ckpt_every, flags)
         if nbytes:
             ckpt = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device)
         rc = lib.ncn_net_fwd(
             x.data_ptr(), xa.data_ptr(), W.data_ptr(), y.data_ptr(), ya.data_ptr(),
             ckpt.data_ptr() if ckpt is not None else None, ckpt_every, B, N, E, n_cache, n_head, first_module, L,
-            float(alpha), activation_code(activation), _dtype_code(x), NCN_RESIDUAL if residual else 0, _stream(),
+            float(alpha), activation_code(activation), _dtype_code(x), flags, _stream(),
         )
     _lib.check("ncn_net_fwd", rc)
     return y, ya, ckpt
 
 
 def net_bwd(s0, s1, dy, dya, W, alpha, activation, n_cache, n_head, first_module=0, ckpt=None, ckpt_every=0,
-            recompute=False, residual=False, want_inputs=False, dW_out: Optional[torch.Tensor] = None):
-    """Backward of net_fwd in one kernel.  (s0, s1) = net output, or net input with recompute.
+            recompute=False, residual=False, want_inputs=False, dW_out: Optional[torch.Tensor] = None, tape=False):
+    """Backward of net_fwd in one kernel.  (s0, s1) = net output, or net input with recompute, or
+    None with tape (the backward then starts from the last state in ckpt).
     Returns (dx, dxa, dW[L, 2E]) (+ rebuilt x, xa with want_inputs).  With dW_out the gradient is
     accumulated into that tensor."""
     lib = _lib.load()
-    _check_inputs(s0, s1, dy, dya)
-    s0, s1, dy, dya = s0.contiguous(), s1.contiguous(), dy.contiguous(), dya.contiguous()
-    B, N, E = s0.shape
+    if tape:
+        if ckpt is None:
+            raise ValueError("tape backward needs the ckpt tensor of net_fwd(..., tape=True)")
+        _check_inputs(dy, dya)
+        s0 = s1 = None
+    else:
+        _check_inputs(s0, s1, dy, dya)
+        s0, s1 = s0.contiguous(), s1.contiguous()
+    dy, dya = dy.contiguous(), dya.contiguous()
+    B, N, E = dy.shape
     L = W.shape[0]
-    W = _weights(W, L * 2 * E, s0.device)
-    dx, dxa = torch.empty_like(s0), torch.empty_like(s0)
-    xr = torch.empty_like(s0) if want_inputs else None
-    xar = torch.empty_like(s0) if want_inputs else None
+    W = _weights(W, L * 2 * E, dy.device)
+    dx, dxa = torch.empty_like(dy), torch.empty_like(dy)
+    xr = torch.empty_like(dy) if want_inputs else None
+    xar = torch.empty_like(dy) if want_inputs else None
     accumulate = dW_out is not None
-    dW = dW_out if accumulate else torch.empty(L, 2 * E, dtype=torch.float32, device=s0.device)
-    flags = (NCN_RECOMPUTE if recompute else 0) | (NCN_RESIDUAL if residual else 0)
-    dt = _dtype_code(s0)
-    with torch.cuda.device(s0.device):
-        ws = _workspace(lib, s0.device, B, N, E, n_cache, n_head, L, dt)
+    dW = dW_out if accumulate else torch.empty(L, 2 * E, dtype=torch.float32, device=dy.device)
+    flags = (NCN_RECOMPUTE if recompute else 0) | (NCN_RESIDUAL if residual else 0) | (NCN_TAPE if tape else 0)
+    dt = _dtype_code(dy)
+    with torch.cuda.device(dy.device):
+        ws = _workspace(lib, dy.device, B, N, E, n_cache, n_head, L, dt)
         rc = lib.ncn_net_bwd(
-            s0.data_ptr(), s1.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(), dxa.data_ptr(),
+            s0.data_ptr() if s0 is not None else None, s1.data_ptr() if s1 is not None else None, dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(), dxa.data_ptr(),
             xr.data_ptr() if want_inputs else None, xar.data_ptr() if want_inputs else None, dW.data_ptr(),
             ckpt.data_ptr() if ckpt is not None else None, ckpt_every, ws.data_ptr(), ws.numel(), B, N, E, n_cache,
             n_head, first_module, L, float(alpha), activation_code(activation), dt, flags, int(accumulate), _stream(),

@@ -18,9 +18,12 @@ from .ncn_pytorch_wrapper_v2 import fused_ncn_net
 
 class NCNResidualStack(nn.Module):
     """`num_layers` layers; layer k is an NCN net of `num_modules` stages with
-    x <- x + net(x, xa).x and xa <- net(x, xa).xa.  weight: [num_layers, num_modules, 2*embed_dim]."""
+    x <- x + net(x, xa).x and xa <- net(x, xa).xa.  weight: [num_layers, num_modules, 2*embed_dim].
+    backward_mode: "recompute" keeps each layer's input and replays its forward in the backward;
+    "tape" keeps the layer's fp32 end state (and periodic ones) instead: no replay, more memory."""
 
-    def __init__(self, num_layers, alpha, activation, n_cache, n_head, num_modules, embed_dim, w_std=None):
+    def __init__(self, num_layers, alpha, activation, n_cache, n_head, num_modules, embed_dim, w_std=None,
+                 backward_mode="recompute"):
         super().__init__()
         self.num_layers = num_layers
         self.alpha = alpha
@@ -28,13 +31,17 @@ class NCNResidualStack(nn.Module):
         self.n_cache = n_cache
         self.n_head = n_head
         self.num_modules = num_modules
+        if backward_mode not in ("recompute", "tape"):
+            raise ValueError("residual layers need backward_mode 'recompute' or 'tape'")
+        self.backward_mode = backward_mode
         std = w_std if w_std is not None else 1 / (2.0 * embed_dim)
         self.weight = nn.Parameter(torch.empty(num_layers, num_modules, 2 * embed_dim).normal_(0.0, std))
 
     def forward(self, x, xa):
         for k in range(self.num_layers):
             x, xa = fused_ncn_net(
-                x, xa, self.weight[k], self.alpha, self.activation_nr, self.n_cache, self.n_head, 0, "recompute", True
+                x, xa, self.weight[k], self.alpha, self.activation_nr, self.n_cache, self.n_head, 0, self.backward_mode,
+                True
             )
         return x, xa
 

@@ -31,8 +31,10 @@ def test_library_exports_every_declared_symbol():
     assert loaded.ncn_version() >= 100
     assert loaded.ncn_status_string(1).decode().startswith("bad shape")
     # pure host arithmetic, no device needed
-    assert loaded.ncn_ckpt_bytes(8, 64, 1, 6, 4) == 1 * 2 * 8 * 64 * 4
-    assert loaded.ncn_ckpt_bytes(8, 64, 1, 4, 4) == 0
+    assert loaded.ncn_ckpt_bytes(8, 64, 1, 6, 4, 0) == 1 * 2 * 8 * 64 * 4
+    assert loaded.ncn_ckpt_bytes(8, 64, 1, 4, 4, 0) == 0
+    assert loaded.ncn_ckpt_bytes(8, 64, 1, 4, 4, 8) == 1 * 2 * 8 * 64 * 4      # tape: the last state
+    assert loaded.ncn_ckpt_bytes(8, 64, 1, 6, 4, 8) == 2 * 2 * 8 * 64 * 4
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
@@ -56,14 +58,18 @@ def test_plan_backward():
     from ncn_cuda_b200.ncn_pytorch_wrapper_v2 import plan_backward
 
     f32, bf16 = torch.float32, torch.bfloat16
-    assert plan_backward(f32, 4, 6, False, "auto") == (False, 4)      # 24 steps -> checkpoint every 4 stages
-    assert plan_backward(f32, 8, 4, False, "auto") == (False, 2)
-    assert plan_backward(f32, 2, 10, False, "auto") == (False, 8)
-    assert plan_backward(f32, 4, 3, False, "auto") == (False, 0)      # 12 steps: nothing to store
-    assert plan_backward(f32, 16, 4, False, "checkpoint") == (False, 1)
-    assert plan_backward(f32, 4, 6, False, "invert") == (False, 0)
-    assert plan_backward(bf16, 16, 4, False, "auto") == (True, 0)
-    assert plan_backward(f32, 8, 4, True, "auto") == (True, 0)
+    assert plan_backward(f32, 4, 6, False, "auto") == (False, 4, False)      # 24 steps -> checkpoint every 4 stages
+    assert plan_backward(f32, 8, 4, False, "auto") == (False, 2, False)
+    assert plan_backward(f32, 2, 10, False, "auto") == (False, 8, False)
+    assert plan_backward(f32, 4, 3, False, "auto") == (False, 0, False)      # 12 steps: nothing to store
+    assert plan_backward(f32, 16, 4, False, "checkpoint") == (False, 1, False)
+    assert plan_backward(f32, 4, 6, False, "invert") == (False, 0, False)
+    assert plan_backward(bf16, 16, 4, False, "auto") == (True, 0, False)
+    assert plan_backward(f32, 8, 4, True, "auto") == (True, 0, False)
+    assert plan_backward(bf16, 16, 4, False, "tape") == (False, 0, True)   # 64 steps from the fp32 end state
+    assert plan_backward(bf16, 16, 8, False, "tape") == (False, 4, True)
+    assert plan_backward(f32, 8, 4, True, "tape") == (False, 2, True)
+    assert plan_backward(f32, 4, 3, True, "tape") == (False, 0, True)
     with pytest.raises(ValueError):
         plan_backward(f32, 8, 4, True, "invert")
     with pytest.raises(ValueError):
