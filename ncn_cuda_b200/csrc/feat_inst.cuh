@@ -1,0 +1,56 @@
+// Explicit instantiation of the register-tiled multi-feature stage kernels (ncn_feat.cuh) for one
+// n_cache (NCN_NC) and one direction (NCN_BWD defined or not); one translation unit each.
+// Head widths d = 4 (one lane per position), 8, 16, 32, 64 (8 features per lane), as far as the
+// group tile fits the registers of a warp (n_cache * d <= 1024).  fp32 storage with the exact tanh,
+// bf16 storage with tanh.approx; every other combination stays with the shared-memory kernels of
+// ncn_generic.cuh.
+#include "ncn_feat.cuh"
+#include "ncn_feat_launch.h"
+
+namespace ncn {
+
+#ifdef NCN_BWD
+#define NCN_KERNEL feat_bwd_kernel
+#else
+#define NCN_KERNEL feat_fwd_kernel
+#endif
+
+template <int LD, int KF, int ACT, typename T>
+static cudaError_t launch_one(const FeatParams& p, int grid, cudaStream_t st, int* occ) {
+  if constexpr (NCN_NC * LD * KF > 1024) {
+    return cudaErrorNotSupported;
+  } else {
+    auto k = NCN_KERNEL<NCN_NC, LD, KF, ACT, T>;
+    if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, kFeatWarps * 32, 0);
+    k<<<grid, kFeatWarps * 32, 0, st>>>(p);
+    return cudaGetLastError();
+  }
+}
+
+template <int LD, int KF>
+static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, int* occ) {
+  if (dtype == DT_F32 && act == ACT_TANH) return launch_one<LD, KF, ACT_TANH, float>(p, grid, st, occ);
+  if (dtype == DT_BF16 && act == ACT_TANH_FAST) return launch_one<LD, KF, ACT_TANH_FAST, __nv_bfloat16>(p, grid, st, occ);
+  return cudaErrorNotSupported;
+}
+
+#define NCN_CAT2(a, b) a##b
+#define NCN_CAT(a, b) NCN_CAT2(a, b)
+#ifdef NCN_BWD
+#define NCN_FN NCN_CAT(launch_feat_bwd_n, NCN_NC)
+#else
+#define NCN_FN NCN_CAT(launch_feat_fwd_n, NCN_NC)
+#endif
+
+cudaError_t NCN_FN(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, int* occ) {
+  switch (d) {
+    case 4: return launch_geo<1, 4>(act, dtype, p, grid, st, occ);
+    case 8: return launch_geo<1, 8>(act, dtype, p, grid, st, occ);
+    case 16: return launch_geo<2, 8>(act, dtype, p, grid, st, occ);
+    case 32: return launch_geo<4, 8>(act, dtype, p, grid, st, occ);
+    case 64: return launch_geo<8, 8>(act, dtype, p, grid, st, occ);
+    default: return cudaErrorNotSupported;
+  }
+}
+
+}  // namespace ncn

@@ -8,6 +8,8 @@
 #include "../../include/ncn_b200.h"
 #include "ncn_generic.cuh"
 #include "ncn_rows_launch.h"
+#include "ncn_feat.cuh"
+#include "ncn_feat_launch.h"
 
 namespace ncn {
 
@@ -343,6 +345,71 @@ static void fill_stage(StageParams& p, int64_t B, int64_t N, int64_t E, int n, i
   p.oma = (float)(1.0 - alpha);
 }
 
+// ---- register-tiled multi-feature stage kernels (ncn_feat.cuh)
+typedef cudaError_t (*FeatLaunchFn)(int, int, int, const FeatParams&, int, cudaStream_t, int*);
+
+static FeatLaunchFn feat_fn(int n, bool bwd) {
+  switch (n) {
+    case 2: return bwd ? launch_feat_bwd_n2 : launch_feat_fwd_n2;
+    case 4: return bwd ? launch_feat_bwd_n4 : launch_feat_fwd_n4;
+    case 8: return bwd ? launch_feat_bwd_n8 : launch_feat_fwd_n8;
+    case 16: return bwd ? launch_feat_bwd_n16 : launch_feat_fwd_n16;
+    case 32: return bwd ? launch_feat_bwd_n32 : launch_feat_fwd_n32;
+    default: return nullptr;
+  }
+}
+
+static long long gcd_ll(long long a, long long b) {
+  while (b) { const long long t = a % b; a = b; b = t; }
+  return a;
+}
+
+// NCN_OK: launched.  NCN_ERR_UNSUPPORTED: no such kernel for these arguments (the caller falls
+// back to the shared-memory kernels); anything else is an error.
+static int launch_feat(bool bwd, const void* const* in, void* const* out, const float* W, float* partials, int64_t B,
+                       int64_t N, int64_t E, int n, int C, int module_l, double alpha, int activation, int dtype,
+                       const DevInfo& dev, cudaStream_t st, int* grid_out) {
+  const int d = (int)(E / C);
+  const int gpw = feat_groups_per_warp(n, d);
+  FeatLaunchFn fn = feat_fn(n, bwd);
+  if (gpw == 0 || fn == nullptr) return NCN_ERR_UNSUPPORTED;
+  if (const char* e = std::getenv("NCN_NO_FEAT")) {  // tuning experiments: force the shared-memory kernels
+    if (e[0] == '1') return NCN_ERR_UNSUPPORTED;
+  }
+  const int act = fused_act(map_act(activation), dtype);
+  for (int q = 0; q < (bwd ? 4 : 2); ++q)
+    if (!aligned16(in[q])) return NCN_ERR_UNSUPPORTED;
+  for (int q = 0; q < (bwd ? 4 : 2); ++q)
+    if (out[q] && !aligned16(out[q])) return NCN_ERR_UNSUPPORTED;
+  FeatParams p{};
+  for (int q = 0; q < 4; ++q) { p.in[q] = in[q]; p.out[q] = out[q]; }
+  p.W = W;
+  p.partials = partials;
+  p.B = B; p.N = (int)N; p.E = (int)E; p.C = C;
+  p.m = (int)(N / n);
+  p.mg = (p.m + gpw - 1) / gpw;
+  p.units = B * p.mg;
+  p.stride = stage_stride(module_l, p.m);
+  p.alpha = (float)alpha;
+  p.oma = (float)(1.0 - alpha);
+  int occ = 0;
+  cudaError_t e = fn(d, act, dtype, p, 0, nullptr, &occ);
+  if (e == cudaErrorNotSupported) return NCN_ERR_UNSUPPORTED;
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (occ < 1) return NCN_ERR_UNSUPPORTED;
+  if (occ > 32) occ = 32;
+  // one warp per (head, unit) at most, a whole number of warps per head
+  long long grid = (p.units * C + kFeatWarps - 1) / kFeatWarps;
+  if (grid > (long long)dev.sms * occ) grid = (long long)dev.sms * occ;
+  const long long q = C / gcd_ll(C, kFeatWarps);
+  grid = (grid + q - 1) / q * q;
+  if (grid > (long long)dev.sms * 32) return NCN_ERR_UNSUPPORTED;  // more heads than the workspace covers
+  e = fn(d, act, dtype, p, (int)grid, st, nullptr);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (grid_out) *grid_out = (int)grid;
+  return NCN_OK;
+}
+
 static size_t workspace_floats(const DevInfo& dev, int64_t E, int L) {
   return (size_t)dev.sms * 32 * 2 * (size_t)E * (size_t)(L < 1 ? 1 : L);
 }
@@ -507,6 +574,13 @@ int ncn_stage_fwd(const void* x, const void* xa, const float* W, void* y, void* 
   }
   DevInfo dev;
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  {
+    const void* fin[4] = {x, xa, nullptr, nullptr};
+    void* fout[4] = {y, ya, nullptr, nullptr};
+    rc = launch_feat(false, fin, fout, W, nullptr, B, N, E, n_cache, n_head, module_l, alpha, activation, dtype, dev,
+                     (cudaStream_t)stream, nullptr);
+    if (rc != NCN_ERR_UNSUPPORTED) return rc;
+  }
   StageParams p{};
   fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
   p.in[0] = x; p.in[1] = xa;
@@ -544,6 +618,15 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
     rc = ncn_net_bwd(y, ya, dy, dya, W, dx, dxa, x_rec, xa_rec, dW, nullptr, 0, workspace, workspace_bytes, B, N, E,
                      n_cache, n_head, module_l, 1, alpha, activation, dtype, 0, 0, stream);
     if (rc != NCN_ERR_SMEM) return rc;
+  }
+  {
+    const void* fin[4] = {y, ya, dy, dya};
+    void* fout[4] = {dx, dxa, x_rec, xa_rec};
+    int fgrid = 0;
+    rc = launch_feat(true, fin, fout, W, static_cast<float*>(workspace), B, N, E, n_cache, n_head, module_l, alpha,
+                     activation, dtype, dev, (cudaStream_t)stream, &fgrid);
+    if (rc == NCN_OK) return reduce_dw(static_cast<float*>(workspace), dW, fgrid, 2 * (int)E, 0, (cudaStream_t)stream);
+    if (rc != NCN_ERR_UNSUPPORTED) return rc;
   }
   StageParams p{};
   fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);

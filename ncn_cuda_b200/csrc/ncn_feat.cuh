@@ -1,0 +1,373 @@
+// Per-stage NCN kernels for several features per position (E > 1, heads of d = E / n_head
+// features), with the whole group tile in registers.
+//
+// Behaviour replaced: ncn_cuda/ncn_fwd_cuda_kernel.cu:28-112 (forward_kernel) and
+// ncn_cuda/ncn_bwd_cuda_kernel.cu:27-229 (backward_kernel), at the shapes the reference's own
+// benchmark uses (grad_test_bench.py:22-28: E = 128, 4 heads, n_cache = 32); math as
+// torch_ref/ncn_pytorch.py:74-94 (step) and torch_ref/ncn_pytorch_invertible.py:97-111, 164-172
+// (inverse, gradient).
+//
+// One warp owns one group (or several small ones) for all its n_cache steps:
+//   lane = (slot, sub): LD = d / KF lanes share a position, each holding KF contiguous features;
+//   the 32 / LD slots of the warp hold the positions, P = n_cache * LD / 32 per lane (position
+//   i = r * SEG + s for slot s, r < P), or several groups side by side when n_cache < 32 / LD.
+// Per step the row x_j reaches every lane by KF shuffles, the dot products over the features are
+// lane-local sums plus log2(LD) exchanges, and no shared memory or barrier is involved.  The
+// kernels are bound by the special-function unit (two instructions per element and step for tanh)
+// like the one-feature kernels.
+#pragma once
+#include "ncn_common.cuh"
+
+namespace ncn {
+
+struct FeatParams {
+  const void* in[4];  // fwd: x, xa ; bwd: y, ya, dy, dya
+  void* out[4];       // fwd: y, ya ; bwd: dx, dxa, x_rec|null, xa_rec|null
+  const float* W;     // [2E]
+  float* partials;    // bwd: [gridDim.x][2E]
+  long long B;
+  long long units;    // B * mg work units per head
+  int N, E, C, m, mg, stride;  // mg = ceil(m / groups per warp)
+  float alpha, oma;
+};
+
+template <int NC, int LD, int KF>
+struct FeatGeom {
+  static_assert(KF % 2 == 0 && 32 % LD == 0, "features are processed in pairs");
+  static constexpr int D = LD * KF;
+  static constexpr int SLOTS = 32 / LD;
+  static constexpr int P = NC >= SLOTS ? NC / SLOTS : 1;  // positions per lane
+  static constexpr int SEG = NC >= SLOTS ? SLOTS : NC;    // slots of one group
+  static constexpr int GPW = SLOTS / SEG;                 // groups per warp
+  static constexpr int KP = KF / 2;
+  static_assert(P * SEG == NC, "n_cache must be a power of two");
+};
+constexpr int kFeatWarps = 8;  // warps per CTA
+
+__device__ __forceinline__ float2 shfl2(float2 v, int src) {
+  return make_float2(__shfl_sync(0xffffffffu, v.x, src), __shfl_sync(0xffffffffu, v.y, src));
+}
+// sum over the LD lanes that share a position
+template <int LD>
+__device__ __forceinline__ float red_sub(float v) {
+#pragma unroll
+  for (int o = 1; o < LD; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+// sum over the SEG slots of a group (lanes LD apart), every lane gets the result
+template <int LD, int SEG>
+__device__ __forceinline__ float red_slots(float v) {
+#pragma unroll
+  for (int o = LD; o < LD * SEG; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int KF, typename T>
+__device__ __forceinline__ void ld_feat(const T* p, float2 (&v)[KF / 2]) {
+  float t[KF];
+  ld_vec<KF>(p, t);
+#pragma unroll
+  for (int q = 0; q < KF / 2; ++q) v[q] = make_float2(t[2 * q], t[2 * q + 1]);
+}
+template <int KF, typename T>
+__device__ __forceinline__ void st_feat(T* p, const float2 (&v)[KF / 2]) {
+  float t[KF];
+#pragma unroll
+  for (int q = 0; q < KF / 2; ++q) { t[2 * q] = v[q].x; t[2 * q + 1] = v[q].y; }
+  st_vec<KF>(p, t);
+}
+
+// Work split shared by both directions: warp -> head c (fixed for the whole kernel, so the
+// weights and the weight-gradient sums of a lane stay in registers), units of that head.
+struct FeatWarp {
+  int c;
+  long long first, step;
+};
+__device__ __forceinline__ FeatWarp feat_warp(const FeatParams& p) {
+  const long long wg = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long tw = (long long)gridDim.x * (blockDim.x >> 5);  // a multiple of C (launch plan)
+  FeatWarp w;
+  w.c = (int)(wg % p.C);
+  w.first = wg / p.C;
+  w.step = tw / p.C;
+  return w;
+}
+
+// ------------------------------------------------------------------------------------------ forward
+template <int NC, int LD, int KF, int ACT, typename T>
+__global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatParams p) {
+  using G = FeatGeom<NC, LD, KF>;
+  using F = ActForm<ACT>;
+  constexpr int P = G::P, SEG = G::SEG, KP = G::KP;
+  constexpr float sT = (float)F::sT;
+  constexpr float cf0 = (float)(kCd * F::f0), cf1 = (float)(kCd * F::f1);
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (LD - 1), slot = lane / LD;
+  const int gw = slot / SEG, s = slot - gw * SEG;
+  const FeatWarp fw = feat_warp(p);
+  const T* gx = static_cast<const T*>(p.in[0]);
+  const T* ga = static_cast<const T*>(p.in[1]);
+  T* gy = static_cast<T*>(p.out[0]);
+  T* gya = static_cast<T*>(p.out[1]);
+
+  // this lane's weights, with (1 - alpha) and the activation's argument scale folded in
+  float2 Wi[KP], Wj[KP];
+  {
+    const float* wi = p.W + fw.c * G::D + sub * KF;
+    const float* wj = wi + p.E;
+    const float f = p.oma * sT;
+#pragma unroll
+    for (int q = 0; q < KP; ++q) {
+      Wi[q] = make_float2(wi[2 * q] * f, wi[2 * q + 1] * f);
+      Wj[q] = make_float2(wj[2 * q] * f, wj[2 * q + 1] * f);
+    }
+  }
+  const float2 alpha_s = f2(p.alpha * sT);
+
+  for (long long u = fw.first; u < p.units; u += fw.step) {
+    const long long b = u / p.mg;
+    const int g = (int)(u - b * p.mg) * G::GPW + gw;
+    const bool valid = g < p.m;
+    float2 X[P][KP], A[P][KP];
+    long long off[P];
+#pragma unroll
+    for (int r = 0; r < P; ++r) {
+      const int i = r * SEG + s;
+      const int blk = (int)(((long long)g + (long long)i * p.stride) % p.m);
+      off[r] = ((b * p.N + (long long)blk * NC + i) * p.E) + fw.c * G::D + sub * KF;
+      if (valid) {
+        ld_feat<KF, T>(gx + off[r], X[r]);
+        ld_feat<KF, T>(ga + off[r], A[r]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < KP; ++q) X[r][q] = A[r][q] = f2(0.0f);
+      }
+    }
+#pragma unroll
+    for (int rj = 0; rj < P; ++rj) {
+#pragma unroll 1
+      for (int sj = 0; sj < SEG; ++sj) {
+        const int src = (gw * SEG + sj) * LD + sub;
+        float2 xj[KP];
+        float2 accj = f2(0.0f);
+#pragma unroll
+        for (int q = 0; q < KP; ++q) {
+          xj[q] = shfl2(X[rj][q], src);
+          accj = __ffma2_rn(xj[q], Wj[q], accj);
+        }
+        const float cj = accj.x + accj.y;
+#pragma unroll
+        for (int r = 0; r < P; ++r) {
+          float2 acc = f2(0.0f);
+#pragma unroll
+          for (int q = 0; q < KP; ++q) acc = __ffma2_rn(X[r][q], Wi[q], acc);
+          const float2 sim = f2(red_sub<LD>(acc.x + acc.y + cj));  // sT (1-alpha)(x_i.Wi + x_j.Wj)
+#pragma unroll
+          for (int q = 0; q < KP; ++q) {
+            const float2 ts = __ffma2_rn(sim, xj[q], __fmul2_rn(X[r][q], alpha_s));
+            const float2 rr = F::r(ts);
+            A[r][q] = __ffma2_rn(rr, f2(cf1), __ffma2_rn(A[r][q], f2(kM), f2(cf0)));
+            X[r][q] = __ffma2_rn(A[r][q], f2(kC), __fmul2_rn(X[r][q], f2(kM)));
+          }
+        }
+      }
+    }
+    if (valid) {
+#pragma unroll
+      for (int r = 0; r < P; ++r) {
+        st_feat<KF, T>(gy + off[r], X[r]);
+        st_feat<KF, T>(gya + off[r], A[r]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ backward
+// From the stage OUTPUT (y, ya) and the cotangents (dy, dya): every step first rebuilds its input
+// by the reversible inverse, then applies the closed-form vector-Jacobian product.  Per step j and
+// position i (features k; sums over k are the dot products):
+//     x_i = (y_i - c ya_i) / m ;  sim_i = (1-alpha)(x_i.Wi + x_j.Wj) ;  T = alpha x_i + sim_i x_j
+//     a_i = (ya_i - c F(T)) / m
+//     gA' = ga + c gy ;  gT = c gA' act'(T) ;  ga <- m gA' ;  gs_i = (1-alpha) gT_i.x_j
+//     gx_i = m gy_i + alpha gT_i + gs_i Wi
+//     gx_j += Wj sum_i gs_i + sum_i sim_i gT_i          (position j in its role as x_j)
+//     dWi += sum_i gs_i x_i ;  dWj += (sum_i gs_i) x_j
+// The weight gradient is summed per lane over all its groups, then over the slots of the warp
+// (fixed shuffle tree), the warps of the CTA that serve the same head (warp order) and the CTAs
+// (dw_reduce_kernel): a fixed order for a given launch shape.
+template <int NC, int LD, int KF, int ACT, typename T>
+__global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatParams p) {
+  using G = FeatGeom<NC, LD, KF>;
+  using F = ActForm<ACT>;
+  constexpr int P = G::P, SEG = G::SEG, KP = G::KP, D = G::D;
+  constexpr float sT = (float)F::sT;
+  constexpr float cds = (float)(kCd * F::ds);                 // gT = cds * gt
+  constexpr float af0 = (float)(-kCd * F::f0 / kMd), af1 = (float)(-kCd * F::f1 / kMd);
+  __shared__ float sdw[kFeatWarps][2][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & (LD - 1), slot = lane / LD;
+  const int gw = slot / SEG, s = slot - gw * SEG;
+  const FeatWarp fw = feat_warp(p);
+  const T* g_y = static_cast<const T*>(p.in[0]);
+  const T* g_ya = static_cast<const T*>(p.in[1]);
+  const T* g_dy = static_cast<const T*>(p.in[2]);
+  const T* g_dya = static_cast<const T*>(p.in[3]);
+  T* g_dx = static_cast<T*>(p.out[0]);
+  T* g_dxa = static_cast<T*>(p.out[1]);
+  T* g_xr = static_cast<T*>(p.out[2]);
+  T* g_xar = static_cast<T*>(p.out[3]);
+
+  float2 Wi[KP], Wj[KP];  // (1 - alpha) folded in
+  {
+    const float* wi = p.W + fw.c * D + sub * KF;
+    const float* wj = wi + p.E;
+#pragma unroll
+    for (int q = 0; q < KP; ++q) {
+      Wi[q] = make_float2(wi[2 * q] * p.oma, wi[2 * q + 1] * p.oma);
+      Wj[q] = make_float2(wj[2 * q] * p.oma, wj[2 * q + 1] * p.oma);
+    }
+  }
+  const float2 alpha_s = f2(p.alpha * sT);
+  const float2 alpha_g = f2(p.alpha * cds);
+  float2 dwi[KP], dwj[KP];  // without the factor (1 - alpha)
+#pragma unroll
+  for (int q = 0; q < KP; ++q) dwi[q] = dwj[q] = f2(0.0f);
+
+  for (long long u = fw.first; u < p.units; u += fw.step) {
+    const long long b = u / p.mg;
+    const int g = (int)(u - b * p.mg) * G::GPW + gw;
+    const bool valid = g < p.m;
+    float2 X[P][KP], A[P][KP], H[P][KP], Gv[P][KP];
+    long long off[P];
+#pragma unroll
+    for (int r = 0; r < P; ++r) {
+      const int i = r * SEG + s;
+      const int blk = (int)(((long long)g + (long long)i * p.stride) % p.m);
+      off[r] = ((b * p.N + (long long)blk * NC + i) * p.E) + fw.c * D + sub * KF;
+      if (valid) {
+        ld_feat<KF, T>(g_y + off[r], X[r]);
+        ld_feat<KF, T>(g_ya + off[r], A[r]);
+        ld_feat<KF, T>(g_dy + off[r], H[r]);
+        ld_feat<KF, T>(g_dya + off[r], Gv[r]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < KP; ++q) X[r][q] = A[r][q] = H[r][q] = Gv[r][q] = f2(0.0f);
+      }
+    }
+#pragma unroll
+    for (int rj = P - 1; rj >= 0; --rj) {
+#pragma unroll 1
+      for (int sj = SEG - 1; sj >= 0; --sj) {
+        const int src = (gw * SEG + sj) * LD + sub;
+        // the step's input x for every position, then the row x_j
+#pragma unroll
+        for (int r = 0; r < P; ++r)
+#pragma unroll
+          for (int q = 0; q < KP; ++q) X[r][q] = __ffma2_rn(A[r][q], f2(-kCoverM), __fmul2_rn(X[r][q], f2(kInvM)));
+        float2 xj[KP];
+        float2 accj = f2(0.0f);
+#pragma unroll
+        for (int q = 0; q < KP; ++q) {
+          xj[q] = shfl2(X[rj][q], src);
+          accj = __ffma2_rn(xj[q], Wj[q], accj);
+        }
+        const float cj = accj.x + accj.y;
+        float2 GT[P][KP];
+        float sim[P], gs[P];
+#pragma unroll
+        for (int r = 0; r < P; ++r) {
+          float2 acc = f2(0.0f);
+#pragma unroll
+          for (int q = 0; q < KP; ++q) acc = __ffma2_rn(X[r][q], Wi[q], acc);
+          sim[r] = red_sub<LD>(acc.x + acc.y + cj);
+          const float2 sim_s = f2(sim[r] * sT);
+          float2 gacc = f2(0.0f);
+#pragma unroll
+          for (int q = 0; q < KP; ++q) {
+            const float2 ts = __ffma2_rn(sim_s, xj[q], __fmul2_rn(X[r][q], alpha_s));
+            const float2 rr = F::r(ts);
+            A[r][q] = __ffma2_rn(rr, f2(af1), __ffma2_rn(A[r][q], f2(kInvM), f2(af0)));
+            const float2 gap = __ffma2_rn(f2(kC), H[r][q], Gv[r][q]);
+            const float2 gt = F::gt(gap, ts, rr);
+            Gv[r][q] = __fmul2_rn(gap, f2(kM));
+            GT[r][q] = gt;
+            gacc = __ffma2_rn(gt, xj[q], gacc);
+          }
+          gs[r] = red_sub<LD>(gacc.x + gacc.y) * cds;  // gT_i . x_j
+        }
+        float2 U[KP];
+#pragma unroll
+        for (int q = 0; q < KP; ++q) U[q] = f2(0.0f);
+        float sl = 0.0f;
+#pragma unroll
+        for (int r = 0; r < P; ++r) {
+          const float2 gsv = f2(gs[r]);
+          const float2 simg = f2(sim[r] * cds);
+          sl += gs[r];
+#pragma unroll
+          for (int q = 0; q < KP; ++q) {
+            H[r][q] = __ffma2_rn(gsv, Wi[q], __ffma2_rn(GT[r][q], alpha_g, __fmul2_rn(H[r][q], f2(kM))));
+            dwi[q] = __ffma2_rn(gsv, X[r][q], dwi[q]);
+            U[q] = __ffma2_rn(simg, GT[r][q], U[q]);
+          }
+        }
+        const float S = red_slots<LD, SEG>(sl);
+        const bool is_j = (s == sj);
+#pragma unroll
+        for (int q = 0; q < KP; ++q) {
+          const float2 col = make_float2(red_slots<LD, SEG>(U[q].x), red_slots<LD, SEG>(U[q].y));
+          if (is_j) {
+            H[rj][q] = __fadd2_rn(H[rj][q], __ffma2_rn(f2(S), Wj[q], col));
+            dwj[q] = __ffma2_rn(f2(S), xj[q], dwj[q]);
+          }
+        }
+      }
+    }
+    if (valid) {
+#pragma unroll
+      for (int r = 0; r < P; ++r) {
+        st_feat<KF, T>(g_dx + off[r], H[r]);
+        st_feat<KF, T>(g_dxa + off[r], Gv[r]);
+        if (g_xr) {
+          st_feat<KF, T>(g_xr + off[r], X[r]);
+          st_feat<KF, T>(g_xar + off[r], A[r]);
+        }
+      }
+    }
+  }
+
+  // ---- weight gradient: slots of the warp, warps of the same head, then the CTA's partial
+#pragma unroll
+  for (int q = 0; q < KP; ++q) {
+#pragma unroll
+    for (int o = LD; o < 32; o <<= 1) {
+      dwi[q].x += __shfl_xor_sync(0xffffffffu, dwi[q].x, o);
+      dwi[q].y += __shfl_xor_sync(0xffffffffu, dwi[q].y, o);
+      dwj[q].x += __shfl_xor_sync(0xffffffffu, dwj[q].x, o);
+      dwj[q].y += __shfl_xor_sync(0xffffffffu, dwj[q].y, o);
+    }
+  }
+  if (slot == 0) {
+#pragma unroll
+    for (int q = 0; q < KP; ++q) {
+      sdw[warp][0][sub * KF + 2 * q] = dwi[q].x * p.oma;
+      sdw[warp][0][sub * KF + 2 * q + 1] = dwi[q].y * p.oma;
+      sdw[warp][1][sub * KF + 2 * q] = dwj[q].x * p.oma;
+      sdw[warp][1][sub * KF + 2 * q + 1] = dwj[q].y * p.oma;
+    }
+  }
+  __syncthreads();
+  const int nwarp = blockDim.x >> 5;
+  for (int idx = threadIdx.x; idx < 2 * p.E; idx += blockDim.x) {
+    const int which = idx / p.E, f = idx - which * p.E;
+    const int c = f / D, k = f - c * D;
+    float acc = 0.0f;
+    for (int w = 0; w < nwarp; ++w) {
+      const long long wg = (long long)blockIdx.x * nwarp + w;
+      if ((int)(wg % p.C) == c) acc += sdw[w][which][k];
+    }
+    p.partials[(long long)blockIdx.x * 2 * p.E + idx] = acc;
+  }
+}
+
+}  // namespace ncn

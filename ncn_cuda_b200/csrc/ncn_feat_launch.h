@@ -1,0 +1,33 @@
+// Host-side entry points of the register-tiled multi-feature stage kernels (one per direction
+// and n_cache).  With occ != nullptr nothing is launched: *occ receives the resident CTAs per SM.
+// cudaErrorNotSupported: no kernel for this (n_cache, d, dtype, activation).
+#pragma once
+#include "ncn_common.cuh"
+
+namespace ncn {
+
+struct FeatParams;
+
+#define NCN_DECL(n)                                                                                          \
+  cudaError_t launch_feat_fwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, \
+                                   int* occ);                                                                 \
+  cudaError_t launch_feat_bwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, \
+                                   int* occ);
+NCN_DECL(2)
+NCN_DECL(4)
+NCN_DECL(8)
+NCN_DECL(16)
+NCN_DECL(32)
+#undef NCN_DECL
+
+// groups a warp works on side by side for (n_cache, d); 0 if there is no kernel
+inline int feat_groups_per_warp(int n, int d) {
+  if (n != 2 && n != 4 && n != 8 && n != 16 && n != 32) return 0;
+  if (d != 4 && d != 8 && d != 16 && d != 32 && d != 64) return 0;
+  if (n * d > 1024) return 0;
+  const int ld = d <= 8 ? 1 : d / 8;
+  const int slots = 32 / ld;
+  return n >= slots ? 1 : slots / n;
+}
+
+}  // namespace ncn

@@ -135,6 +135,73 @@ def test_stage_bf16(ncn):
     assert O.rel_err(y.float(), ry) < TOLBF and O.rel_err(ya.float(), rya) < TOLBF
 
 
+# ---------------------------------------------------------------- several features per position, register-tiled kernels
+FEAT_CASES = [
+    # B, N, E, C, n, module_l        (d = E / C; covered: d in {4, 8, 16, 32, 64}, n * d <= 1024)
+    (3, 64, 8, 2, 2, 1),       # d = 4, sixteen groups per warp
+    (2, 96, 12, 3, 4, 2),      # d = 4, three heads (warps per head not a power of two), m = 24
+    (3, 72, 16, 2, 8, 3),      # d = 8, m = 9: the last warp's group slots are partly empty
+    (2, 128, 32, 2, 16, 2),    # d = 16, one group per warp, one position per lane
+    (2, 128, 32, 1, 32, 1),    # d = 32, four positions per lane
+    (2, 256, 128, 4, 32, 2),   # the reference's own bench shape (grad_test_bench.py:22-28)
+    (2, 64, 64, 1, 16, 3),     # d = 64, four positions per lane
+    (5, 48, 64, 2, 4, 0),      # d = 32, two groups per warp, stage 0 (stride 0)
+    (1, 32, 40, 5, 8, 1),      # d = 8, five heads
+]
+
+
+@pytest.mark.parametrize("B,N,E,C,n,l", FEAT_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feat_stage(ncn, B, N, E, C, n, l, dtype):
+    torch.manual_seed(B * 1000 + N + E + n)
+    x, xa = torch.randn(B, N, E), torch.randn(B, N, E) * 0.3
+    W = torch.randn(2 * E) * (0.5 / (E / C) ** 0.5)
+    dy, dya = torch.randn(B, N, E), torch.randn(B, N, E)
+    if dtype == torch.bfloat16:
+        x, xa, dy, dya = (t.bfloat16().float() for t in (x, xa, dy, dya))
+    xd, xad, Wd = dev(x).to(dtype).requires_grad_(), dev(xa).to(dtype).requires_grad_(), dev(W).requires_grad_()
+    y, ya = ncn.fused_ncn_cuda_v2(xd, xad, Wd, 0.9, 0, n, C, l)
+    xr = x.clone().requires_grad_(); xar = xa.clone().requires_grad_(); Wr = W.clone().requires_grad_()
+    ry, rya = O.stage_forward(xr, xar, Wr, 0.9, "tanh", n, C, l)
+    if dtype == torch.bfloat16:
+        # the backward starts from the bf16-rounded output: judge the forward only, and the
+        # backward against an fp32 run of the same kernels from the same rounded output
+        assert O.rel_err(y.float(), ry) < TOLBF and O.rel_err(ya.float(), rya) < TOLBF
+        yb, yab = y.detach(), ya.detach()
+        got = ncn.ops.stage_bwd(yb, yab, dev(dy).to(dtype), dev(dya).to(dtype), Wd.detach(), 0.9, 0, n, C, l)
+        ref = ncn.ops.stage_bwd(yb.float(), yab.float(), dev(dy), dev(dya), Wd.detach(), 0.9, 0, n, C, l)
+        assert O.rel_err(got[0].float(), ref[0]) < TOLBF and O.rel_err(got[1].float(), ref[1]) < TOLBF
+        assert O.rel_err(got[2], ref[2]) < TOLBF
+        ncn.ops.device_status()
+        return
+    torch.autograd.backward([y, ya], [dev(dy), dev(dya)])
+    torch.autograd.backward([ry, rya], [dy, dya])
+    tol = 3e-5 if n >= 32 else TOL32
+    assert_close((y.detach(), ya.detach(), xd.grad, xad.grad, [Wd.grad]), (ry.detach(), rya.detach(), xr.grad, xar.grad, [Wr.grad]), tol)
+    out = ncn.ops.stage_bwd(y.detach(), ya.detach(), dev(dy), dev(dya), Wd.detach(), 0.9, 0, n, C, l, want_inputs=True)
+    assert O.rel_err(out[3], x) < tol and O.rel_err(out[4], xa) < 10 * tol
+    ncn.ops.device_status()
+
+
+def test_feat_matches_shared_memory_kernels(ncn, monkeypatch):
+    """Same arguments through the register-tiled kernels and (NCN_NO_FEAT=1) the shared-memory ones."""
+    B, N, E, C, n, l = 6, 128, 64, 2, 16, 2
+    torch.manual_seed(17)
+    x, xa = dev(torch.randn(B, N, E)), dev(torch.randn(B, N, E) * 0.3)
+    W = dev(torch.randn(2 * E) * 0.1)
+    dy, dya = dev(torch.randn(B, N, E)), dev(torch.randn(B, N, E))
+    y, ya = ncn.ops.stage_fwd(x, xa, W, 0.9, 0, n, C, l)
+    a = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
+    a2 = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
+    assert all(torch.equal(u, v) for u, v in zip(a, a2))  # reproducible, dW included
+    monkeypatch.setenv("NCN_NO_FEAT", "1")
+    y2, ya2 = ncn.ops.stage_fwd(x, xa, W, 0.9, 0, n, C, l)
+    b = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
+    assert O.rel_err(y, y2) < 2e-6 and O.rel_err(ya, ya2) < 2e-6
+    for u, v in zip(a, b):
+        assert O.rel_err(u, v) < TOL32
+
+
 # ---------------------------------------------------------------- fused nets vs oracle, all modes
 NET_CASES = [
     # B, N, n, L, w_var, activation
