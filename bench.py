@@ -37,6 +37,10 @@ WORKLOADS = {
                  desc="bf16 storage x[262144,8192] g=16 4 stages"),
     "cfg5": dict(B=131072, N=2048, n=8, L=4, w_var=1 / 8, dtype="bf16", act="tanh", seed=4, layers=12, mode="tape",
                  desc="12 residual NCN layers D=2048 g=8 4 stages bf16, 131072 rows per GPU (1/8 of the 8-GPU global batch)"),
+    "ref_e128": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
+                     desc="the reference's own bench shape scaled in rows: x[4096,256,128] 4 heads g=32 3 stages, one kernel per stage"),
+    "ref_e128_small": dict(B=1024, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
+                           desc="ref_e128 with 1024 rows (profiling case)"),
     "small": dict(B=8192, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="tanh", seed=1,
                   desc="cfg2 with 8192 rows (profiling case)"),
 }
@@ -122,14 +126,14 @@ def cpu_rows_per_s(wl, seconds, threads=None, rows=None):
     torch.set_num_threads(threads)
     fixed = rows is not None
     if not fixed:  # first call: spin up the thread pool and autograd before anything is timed
-        xw, xaw, wsw, dyw, dyaw = O.make_inputs(wl["seed"], 4, wl["N"], 1, wl["L"], wl["w_var"])
-        O.net_fwd_bwd(xw, xaw, wsw, dyw, dyaw, 0.9, wl["act"], wl["n"], 1)
+        xw, xaw, wsw, dyw, dyaw = O.make_inputs(wl["seed"], 4, wl["N"], wl.get("E", 1), wl["L"], wl["w_var"])
+        O.net_fwd_bwd(xw, xaw, wsw, dyw, dyaw, 0.9, wl["act"], wl["n"], wl.get("C", 1))
     rows = rows or 8
     dt_run = 0.0
     while True:
-        x, xa, ws, dy, dya = O.make_inputs(wl["seed"], rows, wl["N"], 1, wl["L"], wl["w_var"])
+        x, xa, ws, dy, dya = O.make_inputs(wl["seed"], rows, wl["N"], wl.get("E", 1), wl["L"], wl["w_var"])
         t0 = time.perf_counter()
-        O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, wl["act"], wl["n"], 1)
+        O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, wl["act"], wl["n"], wl.get("C", 1))
         dt_run = time.perf_counter() - t0
         if fixed or dt_run >= seconds / 3 or rows >= wl["B"] or rows >= 4096:
             break
@@ -177,12 +181,13 @@ def run_b200(args, wl, rank, world, local_rank):
     dtype = torch.float32 if wl["dtype"] == "f32" else torch.bfloat16
     w = 4 if wl["dtype"] == "f32" else 2
     B, N, n, L = wl["B"], wl["N"], wl["n"], wl["L"]
+    E, C = wl.get("E", 1), wl.get("C", 1)
     mode = args.mode or wl.get("mode", "auto")
     g = torch.Generator(device=dev).manual_seed(wl["seed"] + 1000 * rank)
-    x = torch.randn(B, N, 1, generator=g, device=dev, dtype=torch.float32).to(dtype).requires_grad_(True)
-    xa = torch.zeros(B, N, 1, device=dev, dtype=dtype).requires_grad_(True)
-    dy = torch.randn(B, N, 1, generator=g, device=dev, dtype=torch.float32).to(dtype)
-    dya = torch.zeros(B, N, 1, device=dev, dtype=dtype)
+    x = torch.randn(B, N, E, generator=g, device=dev, dtype=torch.float32).to(dtype).requires_grad_(True)
+    xa = torch.zeros(B, N, E, device=dev, dtype=dtype).requires_grad_(True)
+    dy = torch.randn(B, N, E, generator=g, device=dev, dtype=torch.float32).to(dtype)
+    dya = torch.zeros(B, N, E, device=dev, dtype=dtype)
     gw = torch.Generator().manual_seed(wl["seed"])
     layers = wl.get("layers", 0)
     if layers:
@@ -190,8 +195,8 @@ def run_b200(args, wl, rank, world, local_rank):
                                    backward_mode="recompute" if mode == "auto" else mode).to(dev)
         ws = [net.weight]
     else:
-        ws = [(torch.randn(2, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]
-        net = ncn.NCNNetTestCuda(0.9, wl["act"], n, 1, L, ws, backward_mode=mode)
+        ws = [(torch.randn(2 * E, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]
+        net = ncn.NCNNetTestCuda(0.9, wl["act"], n, C, L, ws, backward_mode=mode)
 
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
 
@@ -241,16 +246,20 @@ def run_b200(args, wl, rank, world, local_rank):
         peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = 6650.0, "fallback"
-    elems = B * N * max(1, layers)  # every layer of a stack moves the same bytes
+    # every layer of a stack moves the same bytes; with several features per position every STAGE is
+    # its own forward and backward kernel and moves them again
+    per_stage = E > 1
+    elems = B * N * E * max(1, layers) * (L if per_stage else 1)
     bwd_bytes = 6 * w * elems  # reads y, ya, dy, dya; writes dx, dxa
     bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
     step_gbs = 10 * w * elems / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "pair_bwd_wide_kernel (ncn_pairs.cuh)", "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
-        "unit": "GB/s", "frac": bwd_gbs / peak, "ms_per_launch": bwd_ms,
+        "bound": "hbm", "kernel": ("feat_bwd_kernel (ncn_feat.cuh), %d launches per step" % L if per_stage
+                                   else "pair_bwd_wide_kernel (ncn_pairs.cuh)"), "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
+        "unit": "GB/s", "frac": bwd_gbs / peak, "ms_per_launch": bwd_ms / (L if per_stage else 1),
         # measured on the cfg2 shape (fp32, one checkpoint); traffic grows in proportion to the rows
         "traffic": (BWD_TRAFFIC_BYTES_PER_ELEMENT * elems if args.workload in ("cfg2", "small") and mode == "auto" else None),
-        "algorithmic_bytes": bwd_bytes,
+        "algorithmic_bytes": bwd_bytes // (L if per_stage else 1),
         "fwd_plus_bwd": {"achieved": step_gbs, "frac": step_gbs / peak, "frac_of_8TBs_nominal": step_gbs / 8000.0,
                          "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "algorithmic_bytes": 10 * w * elems},
         "note": "issue-bound kernel (n*L dependent tanh steps per element); HBM fraction reported as the metric asks",
@@ -260,13 +269,13 @@ def run_b200(args, wl, rank, world, local_rank):
         "metric": "ncn_fwd_bwd_rows_per_s", "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": wl["desc"], "rows_per_gpu": B, "D": N, "g": n, "stages": L, "activation": wl["act"],
-                   "backward_mode": mode, "parallelism": f"dp{world}", "l2": "inputs larger than L2 (>= 1 GB per tensor)"},
-        "roofline": roofline, "gpu_launches": 3 * args.steps * max(1, layers), "clocks": clocks.summary(),
+        "config": {"workload": wl["desc"], "rows_per_gpu": B, "D": N, "E": E, "heads": C, "g": n, "stages": L, "activation": wl["act"],
+                   "backward_mode": mode, "parallelism": f"dp{world}", "l2": "inputs larger than L2 (%.2f GB per tensor)" % (B * N * E * w / 1e9)},
+        "roofline": roofline, "gpu_launches": (3 * L if per_stage else 3) * args.steps * max(1, layers), "clocks": clocks.summary(),
         "rows_per_s_per_gpu": value / world,
     }
 
-    if rank == 0 and not args.no_e2e and not layers:
+    if rank == 0 and not args.no_e2e and not layers and not per_stage:
         line["e2e"] = run_e2e(ncn, wl, dev, dtype, ws, mode, world)
     if world > 1:
         dist.barrier()

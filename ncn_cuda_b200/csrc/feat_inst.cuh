@@ -1,9 +1,8 @@
 // Explicit instantiation of the register-tiled multi-feature stage kernels (ncn_feat.cuh) for one
 // n_cache (NCN_NC) and one direction (NCN_BWD defined or not); one translation unit each.
 // Head widths d = 4 (one lane per position), 8, 16, 32, 64 (8 features per lane), as far as the
-// group tile fits the registers of a warp (n_cache * d <= 1024).  fp32 storage with the exact tanh,
-// bf16 storage with tanh.approx; every other combination stays with the shared-memory kernels of
-// ncn_generic.cuh.
+// group tile fits the registers of a warp (n_cache * d <= 1024).  Every other shape, and bf16
+// storage with the exact tanh, stays with the shared-memory kernels of ncn_generic.cuh.
 #include "ncn_feat.cuh"
 #include "ncn_feat_launch.h"
 
@@ -29,9 +28,22 @@ static cudaError_t launch_one(const FeatParams& p, int grid, cudaStream_t st, in
 
 template <int LD, int KF>
 static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, int* occ) {
-  if (dtype == DT_F32 && act == ACT_TANH) return launch_one<LD, KF, ACT_TANH, float>(p, grid, st, occ);
-  if (dtype == DT_BF16 && act == ACT_TANH_FAST) return launch_one<LD, KF, ACT_TANH_FAST, __nv_bfloat16>(p, grid, st, occ);
-  return cudaErrorNotSupported;
+  if (dtype == DT_F32) {
+    switch (act) {
+      case ACT_TANH: return launch_one<LD, KF, ACT_TANH, float>(p, grid, st, occ);
+      case ACT_RELU: return launch_one<LD, KF, ACT_RELU, float>(p, grid, st, occ);
+      case ACT_SIGMOID: return launch_one<LD, KF, ACT_SIGMOID, float>(p, grid, st, occ);
+      case ACT_LINEAR: return launch_one<LD, KF, ACT_LINEAR, float>(p, grid, st, occ);
+      default: return cudaErrorNotSupported;
+    }
+  }
+  switch (act) {  // bf16 storage; the exact tanh (NCN_EXACT_TANH=1) stays with the shared-memory kernels
+    case ACT_TANH_FAST: return launch_one<LD, KF, ACT_TANH_FAST, __nv_bfloat16>(p, grid, st, occ);
+    case ACT_RELU: return launch_one<LD, KF, ACT_RELU, __nv_bfloat16>(p, grid, st, occ);
+    case ACT_SIGMOID: return launch_one<LD, KF, ACT_SIGMOID, __nv_bfloat16>(p, grid, st, occ);
+    case ACT_LINEAR: return launch_one<LD, KF, ACT_LINEAR, __nv_bfloat16>(p, grid, st, occ);
+    default: return cudaErrorNotSupported;
+  }
 }
 
 #define NCN_CAT2(a, b) a##b

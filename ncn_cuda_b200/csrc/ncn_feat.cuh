@@ -18,6 +18,10 @@
 #pragma once
 #include "ncn_common.cuh"
 
+#ifndef NCN_FEAT_UNROLL
+#define NCN_FEAT_UNROLL 1
+#endif
+
 namespace ncn {
 
 struct FeatParams {
@@ -43,6 +47,8 @@ struct FeatGeom {
   static_assert(P * SEG == NC, "n_cache must be a power of two");
 };
 constexpr int kFeatWarps = 8;  // warps per CTA
+constexpr int kFeatBwdUnroll = NCN_FEAT_UNROLL;  // backward step loop; 2 measured 10-40 % slower (register spills, code size)
+constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v >> 1); }
 
 __device__ __forceinline__ float2 shfl2(float2 v, int src) {
   return make_float2(__shfl_sync(0xffffffffu, v.x, src), __shfl_sync(0xffffffffu, v.y, src));
@@ -254,73 +260,105 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
         for (int q = 0; q < KP; ++q) X[r][q] = A[r][q] = H[r][q] = Gv[r][q] = f2(0.0f);
       }
     }
+#pragma unroll kFeatBwdUnroll
+    for (int j = NC - 1; j >= 0; --j) {
+      // one body for every step: the row index of x_j inside a lane (rj) is a run-time value,
+      // resolved by selects, so that the code stays small enough for the instruction cache
+      const int rj = j / SEG, sj = j - rj * SEG;
+      const int src = (gw * SEG + sj) * LD + sub;
+      const bool is_j = (s == sj);
+      // the step's input x for every position, then the row x_j
 #pragma unroll
-    for (int rj = P - 1; rj >= 0; --rj) {
-#pragma unroll 1
-      for (int sj = SEG - 1; sj >= 0; --sj) {
-        const int src = (gw * SEG + sj) * LD + sub;
-        // the step's input x for every position, then the row x_j
+      for (int r = 0; r < P; ++r)
+#pragma unroll
+        for (int q = 0; q < KP; ++q) X[r][q] = __ffma2_rn(A[r][q], f2(-kCoverM), __fmul2_rn(X[r][q], f2(kInvM)));
+      float2 xj[KP];
+      float2 accj = f2(0.0f);
+#pragma unroll
+      for (int q = 0; q < KP; ++q) {
+        float2 v = X[0][q];
+#pragma unroll
+        for (int r = 1; r < P; ++r)
+          if (rj == r) v = X[r][q];
+        xj[q] = shfl2(v, src);
+        accj = __ffma2_rn(xj[q], Wj[q], accj);
+      }
+      const float cj = accj.x + accj.y;
+      float gs[P];
+      float u[KF];  // sum_i sim_i gT_i of this lane's positions, per feature
+#pragma unroll
+      for (int k = 0; k < KF; ++k) u[k] = 0.0f;
+#pragma unroll
+      for (int r = 0; r < P; ++r) {
+        float2 acc = f2(0.0f);
+#pragma unroll
+        for (int q = 0; q < KP; ++q) acc = __ffma2_rn(X[r][q], Wi[q], acc);
+        const float sim = red_sub<LD>(acc.x + acc.y + cj);
+        const float2 sim_s = f2(sim * sT), simg = f2(sim * cds);
+        float2 gacc = f2(0.0f);
+#pragma unroll
+        for (int q = 0; q < KP; ++q) {
+          const float2 ts = __ffma2_rn(sim_s, xj[q], __fmul2_rn(X[r][q], alpha_s));
+          const float2 rr = F::r(ts);
+          A[r][q] = __ffma2_rn(rr, f2(af1), __ffma2_rn(A[r][q], f2(kInvM), f2(af0)));
+          const float2 gap = __ffma2_rn(f2(kC), H[r][q], Gv[r][q]);
+          const float2 gt = F::gt(gap, ts, rr);
+          Gv[r][q] = __fmul2_rn(gap, f2(kM));
+          H[r][q] = __ffma2_rn(gt, alpha_g, __fmul2_rn(H[r][q], f2(kM)));  // gs_i Wi is added below
+          gacc = __ffma2_rn(gt, xj[q], gacc);
+          const float2 uu = __ffma2_rn(simg, gt, make_float2(u[2 * q], u[2 * q + 1]));
+          u[2 * q] = uu.x; u[2 * q + 1] = uu.y;
+        }
+        gs[r] = red_sub<LD>(gacc.x + gacc.y) * cds;  // gT_i . x_j
+      }
+      float sl = 0.0f;
+#pragma unroll
+      for (int r = 0; r < P; ++r) {
+        const float2 gsv = f2(gs[r]);
+        sl += gs[r];
+#pragma unroll
+        for (int q = 0; q < KP; ++q) {
+          H[r][q] = __ffma2_rn(gsv, Wi[q], H[r][q]);
+          dwi[q] = __ffma2_rn(gsv, X[r][q], dwi[q]);
+        }
+      }
+      const float S = red_slots<LD, SEG>(sl);
+      // column sums over the group's slots: halving exchange (each round a lane keeps one half of
+      // its values and receives the partner's sums for that half), then the owners hand every
+      // feature's total to the lanes of position j
+      constexpr int ROUNDS = (KF < SEG) ? ilog2(KF) : ilog2(SEG);
+      constexpr int LEFT = KF >> ROUNDS;  // values a lane still holds
+#pragma unroll
+      for (int t = 0; t < ROUNDS; ++t) {
+        const int half = KF >> (t + 1);
+        const bool up = ((s >> t) & 1) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+          const float keep = up ? u[i + half] : u[i];
+          const float send = up ? u[i] : u[i + half];
+          u[i] = keep + __shfl_xor_sync(0xffffffffu, send, LD << t);
+        }
+      }
+      if constexpr (LEFT == 1) {
+#pragma unroll
+        for (int o = LD << ROUNDS; o < LD * SEG; o <<= 1) u[0] += __shfl_xor_sync(0xffffffffu, u[0], o);
+      }
+      const int base = lane - ((s & ((1 << ROUNDS) - 1)) * LD);
+      float col[KF];
+#pragma unroll
+      for (int f = 0; f < KF; ++f) {
+        int owner = 0;  // slot bits of the lane that ends up with feature f
+#pragma unroll
+        for (int t = 0; t < ROUNDS; ++t) owner |= ((f / (KF >> (t + 1))) & 1) << t;
+        col[f] = __shfl_sync(0xffffffffu, u[f % LEFT], base + owner * LD);
+      }
+#pragma unroll
+      for (int q = 0; q < KP; ++q) {
+        const float2 add = __ffma2_rn(f2(S), Wj[q], make_float2(col[2 * q], col[2 * q + 1]));
 #pragma unroll
         for (int r = 0; r < P; ++r)
-#pragma unroll
-          for (int q = 0; q < KP; ++q) X[r][q] = __ffma2_rn(A[r][q], f2(-kCoverM), __fmul2_rn(X[r][q], f2(kInvM)));
-        float2 xj[KP];
-        float2 accj = f2(0.0f);
-#pragma unroll
-        for (int q = 0; q < KP; ++q) {
-          xj[q] = shfl2(X[rj][q], src);
-          accj = __ffma2_rn(xj[q], Wj[q], accj);
-        }
-        const float cj = accj.x + accj.y;
-        float2 GT[P][KP];
-        float sim[P], gs[P];
-#pragma unroll
-        for (int r = 0; r < P; ++r) {
-          float2 acc = f2(0.0f);
-#pragma unroll
-          for (int q = 0; q < KP; ++q) acc = __ffma2_rn(X[r][q], Wi[q], acc);
-          sim[r] = red_sub<LD>(acc.x + acc.y + cj);
-          const float2 sim_s = f2(sim[r] * sT);
-          float2 gacc = f2(0.0f);
-#pragma unroll
-          for (int q = 0; q < KP; ++q) {
-            const float2 ts = __ffma2_rn(sim_s, xj[q], __fmul2_rn(X[r][q], alpha_s));
-            const float2 rr = F::r(ts);
-            A[r][q] = __ffma2_rn(rr, f2(af1), __ffma2_rn(A[r][q], f2(kInvM), f2(af0)));
-            const float2 gap = __ffma2_rn(f2(kC), H[r][q], Gv[r][q]);
-            const float2 gt = F::gt(gap, ts, rr);
-            Gv[r][q] = __fmul2_rn(gap, f2(kM));
-            GT[r][q] = gt;
-            gacc = __ffma2_rn(gt, xj[q], gacc);
-          }
-          gs[r] = red_sub<LD>(gacc.x + gacc.y) * cds;  // gT_i . x_j
-        }
-        float2 U[KP];
-#pragma unroll
-        for (int q = 0; q < KP; ++q) U[q] = f2(0.0f);
-        float sl = 0.0f;
-#pragma unroll
-        for (int r = 0; r < P; ++r) {
-          const float2 gsv = f2(gs[r]);
-          const float2 simg = f2(sim[r] * cds);
-          sl += gs[r];
-#pragma unroll
-          for (int q = 0; q < KP; ++q) {
-            H[r][q] = __ffma2_rn(gsv, Wi[q], __ffma2_rn(GT[r][q], alpha_g, __fmul2_rn(H[r][q], f2(kM))));
-            dwi[q] = __ffma2_rn(gsv, X[r][q], dwi[q]);
-            U[q] = __ffma2_rn(simg, GT[r][q], U[q]);
-          }
-        }
-        const float S = red_slots<LD, SEG>(sl);
-        const bool is_j = (s == sj);
-#pragma unroll
-        for (int q = 0; q < KP; ++q) {
-          const float2 col = make_float2(red_slots<LD, SEG>(U[q].x), red_slots<LD, SEG>(U[q].y));
-          if (is_j) {
-            H[rj][q] = __fadd2_rn(H[rj][q], __ffma2_rn(f2(S), Wj[q], col));
-            dwj[q] = __ffma2_rn(f2(S), xj[q], dwj[q]);
-          }
-        }
+          if (is_j && rj == r) H[r][q] = __fadd2_rn(H[r][q], add);
+        if (is_j) dwj[q] = __ffma2_rn(f2(S), xj[q], dwj[q]);
       }
     }
     if (valid) {

@@ -183,6 +183,31 @@ def test_feat_stage(ncn, B, N, E, C, n, l, dtype):
     ncn.ops.device_status()
 
 
+@pytest.mark.parametrize("act", ["relu", "sigmoid", "linear"])
+@pytest.mark.parametrize("B,N,E,C,n,l", [(2, 128, 32, 1, 32, 1), (3, 72, 16, 2, 8, 3), (2, 64, 64, 1, 16, 2)])
+def test_feat_activations(ncn, B, N, E, C, n, l, act):
+    torch.manual_seed(N + E + n)
+    x, xa = torch.randn(B, N, E), torch.randn(B, N, E) * 0.3
+    W = torch.randn(2 * E) * (0.5 / (E / C) ** 0.5)
+    dy, dya = torch.randn(B, N, E), torch.randn(B, N, E)
+    code = ncn.ops.ACTIVATION_CODES[act]
+    xd, xad, Wd = dev(x).requires_grad_(), dev(xa).requires_grad_(), dev(W).requires_grad_()
+    y, ya = ncn.fused_ncn_cuda_v2(xd, xad, Wd, 0.9, code, n, C, l)
+    torch.autograd.backward([y, ya], [dev(dy), dev(dya)])
+    xr = x.clone().requires_grad_(); xar = xa.clone().requires_grad_(); Wr = W.clone().requires_grad_()
+    ry, rya = O.stage_forward(xr, xar, Wr, 0.9, act, n, C, l)
+    torch.autograd.backward([ry, rya], [dy, dya])
+    if act == "relu":
+        # the rebuilt x differs from the forward's by rounding, so a T within ~1e-6 of 0 can land on
+        # the other side of the kink: compare the forward strictly, the gradients in the mean
+        assert O.rel_err(y, ry) < TOL32 and O.rel_err(ya, rya) < TOL32
+        assert O.rel_err(xd.grad, xr.grad) < 1e-3 and O.rel_err(Wd.grad, Wr.grad) < 1e-3
+    else:
+        tol = 3e-5 if n >= 32 else TOL32
+        assert_close((y.detach(), ya.detach(), xd.grad, xad.grad, [Wd.grad]), (ry.detach(), rya.detach(), xr.grad, xar.grad, [Wr.grad]), tol)
+    ncn.ops.device_status()
+
+
 def test_feat_matches_shared_memory_kernels(ncn, monkeypatch):
     """Same arguments through the register-tiled kernels and (NCN_NO_FEAT=1) the shared-memory ones."""
     B, N, E, C, n, l = 6, 128, 64, 2, 16, 2
