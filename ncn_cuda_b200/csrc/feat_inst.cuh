@@ -1,6 +1,6 @@
 // Explicit instantiation of the register-tiled multi-feature stage kernels (ncn_feat.cuh) for one
 // n_cache (NCN_NC) and one direction (NCN_BWD defined or not); one translation unit each.
-// Head widths d = 4 (one lane per position), 8, 16, 32, 64 (8 features per lane), as far as the
+// Head widths d = 2, 4 (one lane per position), 8, 16, 32, 64, 128 (8 features per lane), as far as the
 // group tile fits the registers of a warp (n_cache * d <= 1024).  Every other shape, and bf16
 // storage with the exact tanh, stays with the shared-memory kernels of ncn_generic.cuh.
 #include "ncn_feat.cuh"
@@ -56,11 +56,13 @@ static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid,
 
 cudaError_t NCN_FN(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, int* occ) {
   switch (d) {
+    case 2: return launch_geo<1, 2>(act, dtype, p, grid, st, occ);
     case 4: return launch_geo<1, 4>(act, dtype, p, grid, st, occ);
     case 8: return launch_geo<1, 8>(act, dtype, p, grid, st, occ);
     case 16: return launch_geo<2, 8>(act, dtype, p, grid, st, occ);
     case 32: return launch_geo<4, 8>(act, dtype, p, grid, st, occ);
     case 64: return launch_geo<8, 8>(act, dtype, p, grid, st, occ);
+    case 128: return launch_geo<16, 8>(act, dtype, p, grid, st, occ);
     default: return cudaErrorNotSupported;
   }
 }

@@ -23,7 +23,7 @@ NCN_DECL(32)
 // groups a warp works on side by side for (n_cache, d); 0 if there is no kernel
 inline int feat_groups_per_warp(int n, int d) {
   if (n != 2 && n != 4 && n != 8 && n != 16 && n != 32) return 0;
-  if (d != 4 && d != 8 && d != 16 && d != 32 && d != 64) return 0;
+  if (d != 2 && d != 4 && d != 8 && d != 16 && d != 32 && d != 64 && d != 128) return 0;
   if (n * d > 1024) return 0;
   const int ld = d <= 8 ? 1 : d / 8;
   const int slots = 32 / ld;

@@ -137,7 +137,7 @@ def test_stage_bf16(ncn):
 
 # ---------------------------------------------------------------- several features per position, register-tiled kernels
 FEAT_CASES = [
-    # B, N, E, C, n, module_l        (d = E / C; covered: d in {4, 8, 16, 32, 64}, n * d <= 1024)
+    # B, N, E, C, n, module_l        (d = E / C; covered: d in {2, 4, ..., 128}, n * d <= 1024)
     (3, 64, 8, 2, 2, 1),       # d = 4, sixteen groups per warp
     (2, 96, 12, 3, 4, 2),      # d = 4, three heads (warps per head not a power of two), m = 24
     (3, 72, 16, 2, 8, 3),      # d = 8, m = 9: the last warp's group slots are partly empty
@@ -147,6 +147,9 @@ FEAT_CASES = [
     (2, 64, 64, 1, 16, 3),     # d = 64, four positions per lane
     (5, 48, 64, 2, 4, 0),      # d = 32, two groups per warp, stage 0 (stride 0)
     (1, 32, 40, 5, 8, 1),      # d = 8, five heads
+    (2, 64, 4, 2, 4, 1),       # d = 2, one feature pair per lane
+    (2, 32, 128, 1, 8, 2),     # d = 128: sixteen lanes per position, four positions per lane
+    (3, 16, 256, 2, 2, 1),     # d = 128, n = 2
 ]
 
 
