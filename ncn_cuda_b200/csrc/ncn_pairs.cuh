@@ -320,6 +320,168 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_fwd_kernel(const RowsParams p
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Forward with ONE tile buffer and two pairs per thread: the TMA loads land in the buffer in native
+// layout, the stage-local (x, a) slots overwrite it in place and the native results are staged in
+// it for the TMA stores ("all threads read, barrier, all threads write" at the two changes of
+// layout; a thread's two pairs fit in registers across the barrier).  A tile then costs 8 bytes
+// per position, so four CTAs of half the threads fit one SM: four independent barrier domains
+// whose stage boundaries and copies overlap each other's arithmetic.  With F_RESIDUAL a second
+// native copy of x is kept for the final add.
+template <int NG, int ACT, typename T, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) pair_fwd_dual_kernel(const RowsParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  using F = ActForm<ACT>;
+  constexpr int PPT = 2;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int N = p.N, m = p.m, R = p.R, L = p.L;
+  const int mh = m >> 1;
+  const int RN = R * N;
+  T* win = reinterpret_cast<T*>(smem + p.off_work);  // native x at win, xa at win + RN
+  const uint32_t work_addr = smem_u32(smem + p.off_work);
+  T* sres = reinterpret_cast<T*>(smem + p.off_in[0]);  // F_RESIDUAL: native x of the tile
+  StageRec* recs = reinterpret_cast<StageRec*>(smem + p.off_w);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + p.off_bar);
+  int* abort_flag = reinterpret_cast<int*>(bar + 2);
+  const T* gx_in = static_cast<const T*>(p.in[0]);
+  const T* ga_in = static_cast<const T*>(p.in[1]);
+  T* gy_out = static_cast<T*>(p.out[0]);
+  T* gya_out = static_cast<T*>(p.out[1]);
+  float2* ckpt = reinterpret_cast<float2*>(p.ckpt);
+  const bool residual = (p.flags & F_RESIDUAL) != 0;
+  const long long BN = p.B * (long long)N;
+
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  fill_stage_table(recs, p, ckpt != nullptr, tid, nthr);
+  __syncthreads();
+
+  auto issue_load = [&](long long tl) {
+    const long long row0 = tl * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
+    mbar_expect_tx(&bar[0], (residual ? 3 : 2) * bytes);
+    bulk_g2s(win, gx_in + row0 * N, bytes, &bar[0]);
+    bulk_g2s(win + RN, ga_in + row0 * N, bytes, &bar[0]);
+    if (residual) bulk_g2s(sres, gx_in + row0 * N, bytes, &bar[0]);
+  };
+
+  uint32_t phase = 0;
+  int rr[PPT], tt[PPT], base[PPT];
+  uint32_t wrow[PPT];
+#pragma unroll
+  for (int pp = 0; pp < PPT; ++pp) {
+    const int item = tid + pp * nthr;
+    rr[pp] = item / mh;
+    tt[pp] = item - rr[pp] * mh;
+    base[pp] = rr[pp] * N;
+    wrow[pp] = work_addr + ((uint32_t)base[pp] << 3);
+  }
+  constexpr float sT = (float)F::sT;
+  PairW w;
+  w.alpha = f2(p.alpha * sT);
+
+  for (long long tile = blockIdx.x; tile < p.tiles; tile += gridDim.x) {
+    if (tid == 0) {
+      bulk_wait_read0();  // the previous tile's stores have left the buffer
+      issue_load(tile);
+    }
+    if (!mbar_wait_bounded(&bar[0], phase)) *abort_flag = 1;
+    phase ^= 1;
+    __syncthreads();
+    if (*abort_flag) break;
+
+    const long long row0 = tile * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    bool active[PPT];
+#pragma unroll
+    for (int pp = 0; pp < PPT; ++pp) active[pp] = rr[pp] < rows;
+
+    float2 X[PPT][NG], A[PPT][NG];
+    uint32_t aa[NG], ab[NG];
+
+    StageRec rec_next = recs[0];
+    for (int l = 0; l < L; ++l) {
+      const StageRec rec = rec_next;
+      if (l + 1 < L) rec_next = recs[l + 1];
+      const int s = rec.s;
+      const bool first = (l == 0), last = (l == L - 1);
+      w.owi = f2(rec.owi * sT);
+      w.owj = f2(rec.owj * sT);
+      if (first) {
+#pragma unroll
+        for (int pp = 0; pp < PPT; ++pp)
+          if (active[pp]) {
+            ld_native_pair<NG, T>(win + base[pp], tt[pp], s, m, X[pp]);
+            ld_native_pair<NG, T>(win + RN + base[pp], tt[pp], s, m, A[pp]);
+          }
+        __syncthreads();  // native inputs are in registers; the buffer may now take slots
+      }
+#pragma unroll
+      for (int pp = 0; pp < PPT; ++pp) {
+        if (active[pp]) {
+          pair_addrs<NG, 3>(wrow[pp], tt[pp], s, m, aa, ab);
+          if (!first) {
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              const float2 va = lds64(aa[o]);
+              const float2 vb = lds64(ab[o]);
+              X[pp][o] = make_float2(va.x, vb.x);
+              A[pp][o] = make_float2(va.y, vb.y);
+            }
+          }
+          pair_forward<NG, ACT>(X[pp], A[pp], w);
+          if (rec.ck >= 0) {  // filed under this stage's groups: the backward of this stage reads o*m + g
+            float2* ck = ckpt + row0 * N + base[pp] + (long long)rec.ck * BN + tt[pp];
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              ck[o * m] = make_float2(X[pp][o].x, A[pp][o].x);
+              ck[o * m + mh] = make_float2(X[pp][o].y, A[pp][o].y);
+            }
+          }
+          if (!last) {
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              sts64(aa[o], X[pp][o].x, A[pp][o].x);
+              sts64(ab[o], X[pp][o].y, A[pp][o].y);
+            }
+          }
+        }
+      }
+      if (last) {
+        __syncthreads();  // every slot has been read; the buffer may now take the native results
+#pragma unroll
+        for (int pp = 0; pp < PPT; ++pp)
+          if (active[pp]) {
+            if (residual) {
+              float2 xin[NG];
+              ld_native_pair<NG, T>(sres + base[pp], tt[pp], s, m, xin);
+#pragma unroll
+              for (int o = 0; o < NG; ++o) X[pp][o] = fadd2(X[pp][o], xin[o]);
+            }
+            st_native_pair<NG, T>(win + base[pp], tt[pp], s, m, X[pp]);
+            st_native_pair<NG, T>(win + RN + base[pp], tt[pp], s, m, A[pp]);
+          }
+        fence_proxy_async();
+      }
+      __syncthreads();
+    }
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
+      bulk_s2g(gy_out + row0 * N, win, bytes);
+      bulk_s2g(gya_out + row0 * N, win + RN, bytes);
+      bulk_commit();
+    }
+  }
+  if (tid == 0) {
+    bulk_wait_all0();
+    if (*abort_flag) atomicExch(p.status, DEV_WAIT_TIMEOUT);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ backward
 // Shared memory per tile is cut to the minimum so that two CTAs fit one SM (their barriers are
 // independent, so one CTA computes while the other is in a stage boundary or waiting for copies):
@@ -514,6 +676,199 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_bwd_kernel(const RowsParams p
           sts128(aa[o], X[o].x, A[o].x, H[o].x, G[o].x);
           sts128(ab[o], X[o].y, A[o].y, H[o].y, G[o].y);
         }
+      }
+      // ---- weight-gradient partial of this stage: fixed-order warp tree, one slot per warp
+      {
+        const float di = dwi.x + dwi.y, dj = dwj.x + dwj.y;
+        const bool hi = (lane & 16) != 0;
+        const float give = hi ? di : dj;
+        float keep = hi ? dj : di;
+        keep += __shfl_xor_sync(0xffffffffu, give, 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o);
+        if ((lane & 15) == 0) red[(l * nwarp + warp) * 2 + (hi ? 1 : 0)] += keep;
+      }
+      if (last) fence_proxy_async();
+      __syncthreads();
+    }
+    if (tid == 0) {
+      const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
+      bulk_s2g(static_cast<T*>(p.out[0]) + row0 * N, win, bytes);
+      bulk_s2g(static_cast<T*>(p.out[1]) + row0 * N, win + RN, bytes);
+      if (want_rec) {
+        bulk_s2g(static_cast<T*>(p.out[2]) + row0 * N, win + 2 * RN, bytes);
+        bulk_s2g(static_cast<T*>(p.out[3]) + row0 * N, win + 3 * RN, bytes);
+      }
+      bulk_commit();
+    }
+  }
+  // ---- per-CTA partial: sum the warp slots in warp order
+  __syncthreads();
+  for (int i = tid; i < 2 * L; i += nthr) {
+    const int l = i >> 1, c = i & 1;
+    float acc = 0.0f;
+    for (int w2 = 0; w2 < nwarp; ++w2) acc += red[(l * nwarp + w2) * 2 + c];
+    p.partials[(long long)blockIdx.x * 2 * L + i] = acc;
+  }
+  if (tid == 0) {
+    bulk_wait_all0();
+    if (*abort_flag) atomicExch(p.status, DEV_WAIT_TIMEOUT);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Backward, aliased tile buffer with TWO pairs per thread: half the threads of pair_bwd_kernel for
+// the same tile, so that two CTAs fit one SM with a full register budget (no spills) and one
+// CTA's stage barriers overlap the other's arithmetic.  Plain backward only (from the net output,
+// checkpoints allowed): no replay, no residual, no tape.
+template <int NG, int ACT, typename T, int MAXT>
+__global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  using F = ActForm<ACT>;
+  constexpr int PPT = 2;
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarp = (nthr + 31) >> 5;
+  const int N = p.N, m = p.m, R = p.R, L = p.L;
+  const int mh = m >> 1;
+  const int RN = R * N;
+  T* win = reinterpret_cast<T*>(smem + p.off_work);  // native streams q at win + q*RN
+  const uint32_t work_addr = smem_u32(smem + p.off_work);
+  float2* sck = reinterpret_cast<float2*>(smem + p.off_ckpt);
+  float* red = reinterpret_cast<float*>(smem + p.off_red);  // [L][nwarp][2]
+  StageRec* recs = reinterpret_cast<StageRec*>(smem + p.off_w);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + p.off_bar);
+  int* abort_flag = reinterpret_cast<int*>(bar + 2);
+  const T* g_in[4] = {static_cast<const T*>(p.in[0]), static_cast<const T*>(p.in[1]), static_cast<const T*>(p.in[2]),
+                      static_cast<const T*>(p.in[3])};
+  const float2* ckpt = reinterpret_cast<const float2*>(p.ckpt);
+  const bool want_rec = p.out[2] != nullptr;
+  const long long BN = p.B * (long long)N;
+  const uint32_t n_ck = p.n_ckpt_slots;
+
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  fill_stage_table(recs, p, ckpt != nullptr, tid, nthr);
+  for (int i = tid; i < 2 * L * nwarp; i += nthr) red[i] = 0.0f;
+  __syncthreads();
+
+  auto issue_load = [&](long long tl) {
+    const long long row0 = tl * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
+    const uint32_t cbytes = (uint32_t)(rows * N * sizeof(float2));
+    mbar_expect_tx(&bar[0], 4 * bytes + n_ck * cbytes);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) bulk_g2s(win + q * RN, g_in[q] + row0 * N, bytes, &bar[0]);
+    for (uint32_t k = 0; k < n_ck; ++k) bulk_g2s(sck + k * RN, ckpt + (long long)k * BN + row0 * N, cbytes, &bar[0]);
+  };
+
+  uint32_t phase = 0;
+  int rr[PPT], tt[PPT], base[PPT];
+  uint32_t wrow[PPT];
+#pragma unroll
+  for (int pp = 0; pp < PPT; ++pp) {
+    const int item = tid + pp * nthr;
+    rr[pp] = item / mh;
+    tt[pp] = item - rr[pp] * mh;
+    base[pp] = rr[pp] * N;
+    wrow[pp] = work_addr + ((uint32_t)base[pp] << 4);
+  }
+  constexpr float sT = (float)F::sT;
+  PairWB w;
+  w.alpha = f2(p.alpha);
+  w.oma = f2(p.oma);
+
+  for (long long tile = blockIdx.x; tile < p.tiles; tile += gridDim.x) {
+    if (tid == 0) {
+      bulk_wait_read0();  // the previous tile's stores have left W
+      issue_load(tile);
+    }
+    if (!mbar_wait_bounded(&bar[0], phase)) *abort_flag = 1;
+    phase ^= 1;
+    __syncthreads();
+    if (*abort_flag) break;
+
+    const long long row0 = tile * R;
+    const int rows = (int)min((long long)R, p.B - row0);
+    bool active[PPT];
+#pragma unroll
+    for (int pp = 0; pp < PPT; ++pp) active[pp] = rr[pp] < rows;
+
+    float2 X[PPT][NG], A[PPT][NG], H[PPT][NG], G[PPT][NG];
+    uint32_t aa[NG], ab[NG];
+
+    StageRec rec_next = recs[L - 1];
+    for (int l = L - 1; l >= 0; --l) {
+      const StageRec rec = rec_next;
+      if (l > 0) rec_next = recs[l - 1];
+      const int s = rec.s;
+      const bool first = (l == L - 1), last = (l == 0);
+      w.owi = f2(rec.owi);
+      w.owj = f2(rec.owj);
+      w.owjs = f2(rec.owj * sT);
+      float2 dwi = f2(0.0f), dwj = f2(0.0f);
+
+      if (first) {
+#pragma unroll
+        for (int pp = 0; pp < PPT; ++pp)
+          if (active[pp]) {
+            const T* s0 = win + base[pp];
+            ld_native_pair<NG, T>(s0, tt[pp], s, m, X[pp]);
+            ld_native_pair<NG, T>(s0 + RN, tt[pp], s, m, A[pp]);
+            ld_native_pair<NG, T>(s0 + 2 * RN, tt[pp], s, m, H[pp]);
+            ld_native_pair<NG, T>(s0 + 3 * RN, tt[pp], s, m, G[pp]);
+          }
+        __syncthreads();  // native inputs are in registers; W may now take slots
+      }
+#pragma unroll
+      for (int pp = 0; pp < PPT; ++pp) {
+        if (active[pp]) {
+          pair_addrs<NG, 4>(wrow[pp], tt[pp], s, m, aa, ab);
+          if (!first) {
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              const float4 va = lds128(aa[o]), vb = lds128(ab[o]);
+              X[pp][o] = make_float2(va.x, vb.x);
+              A[pp][o] = make_float2(va.y, vb.y);
+              H[pp][o] = make_float2(va.z, vb.z);
+              G[pp][o] = make_float2(va.w, vb.w);
+            }
+            if (rec.ck >= 0) {  // a state saved after stage l replaces the rebuilt one
+              const float2* c = sck + rec.ck * RN + base[pp] + tt[pp];
+#pragma unroll
+              for (int o = 0; o < NG; ++o) {
+                const float2 va = c[o * m], vb = c[o * m + mh];
+                X[pp][o] = make_float2(va.x, vb.x);
+                A[pp][o] = make_float2(va.y, vb.y);
+              }
+            }
+          }
+          pair_backward<NG, ACT>(X[pp], A[pp], H[pp], G[pp], w, dwi, dwj);
+          if (!last) {
+#pragma unroll
+            for (int o = 0; o < NG; ++o) {
+              sts128(aa[o], X[pp][o].x, A[pp][o].x, H[pp][o].x, G[pp][o].x);
+              sts128(ab[o], X[pp][o].y, A[pp][o].y, H[pp][o].y, G[pp][o].y);
+            }
+          }
+        }
+      }
+      if (last) {
+        __syncthreads();  // every slot has been read; W may now take the native results
+#pragma unroll
+        for (int pp = 0; pp < PPT; ++pp)
+          if (active[pp]) {
+            T* wout = win + base[pp];
+            st_native_pair<NG, T>(wout, tt[pp], s, m, H[pp]);
+            st_native_pair<NG, T>(wout + RN, tt[pp], s, m, G[pp]);
+            if (want_rec) {
+              st_native_pair<NG, T>(wout + 2 * RN, tt[pp], s, m, X[pp]);
+              st_native_pair<NG, T>(wout + 3 * RN, tt[pp], s, m, A[pp]);
+            }
+          }
       }
       // ---- weight-gradient partial of this stage: fixed-order warp tree, one slot per warp
       {

@@ -16,12 +16,34 @@ namespace ncn {
 template <int ACT, typename T>
 static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st, int* occ) {
 #ifdef NCN_BWD
+  if (p.variant == 2) {
+    if constexpr (NCN_NG <= 8) {
+      auto kd = pair_bwd_dual_kernel<NCN_NG, ACT, T, NCN_CFG::threads / 2>;
+      cudaError_t ed = cudaFuncSetAttribute(kd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (ed != cudaSuccess) return ed;
+      if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kd, threads, smem);
+      kd<<<grid, threads, smem, st>>>(p);
+      return cudaGetLastError();
+    } else {
+      return cudaErrorNotSupported;
+    }
+  }
   if (p.variant == 1) {
     auto kw = pair_bwd_wide_kernel<NCN_NG, ACT, T, NCN_CFG::threads>;
     cudaError_t ew = cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ew != cudaSuccess) return ew;
     if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kw, threads, smem);
     kw<<<grid, threads, smem, st>>>(p);
+    return cudaGetLastError();
+  }
+#endif
+#ifndef NCN_BWD
+  if (p.variant == 2) {
+    auto kd = pair_fwd_dual_kernel<NCN_NG, ACT, T, NCN_CFG::threads / 2, (NCN_NG <= 8 ? 4 : 2)>;
+    cudaError_t ed = cudaFuncSetAttribute(kd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ed != cudaSuccess) return ed;
+    if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kd, threads, smem);
+    kd<<<grid, threads, smem, st>>>(p);
     return cudaGetLastError();
   }
 #endif
