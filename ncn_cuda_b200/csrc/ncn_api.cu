@@ -132,10 +132,10 @@ static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, i
   const char* nopair = std::getenv("NCN_NO_PAIR");
   pl.pair = pair_fn(n, bwd) != nullptr && m % 2 == 0 && m / 2 <= pair_max_threads(n, bwd) && !(nopair && nopair[0] == '1');
   const bool wide = bwd && pl.pair && want_wide && !want_dual;
-  const bool dual = bwd && pl.pair && want_dual && n <= 8 && !(flags & (F_RECOMPUTE | F_RESIDUAL | F_TAPE));
+  const bool dual = bwd && pl.pair && want_dual && n <= 8 && !(flags & F_RECOMPUTE);
   if (want_dual && (bwd ? !dual : !pl.pair)) return NCN_ERR_UNSUPPORTED;
   if (wide) pl.variant = 1;  // separate buffers: planned by the general layout below
-  if (pl.pair && bwd && !wide && (flags & F_TAPE)) pl.pair = false;  // the aliased variant has no tape path
+  if (pl.pair && bwd && !wide && !dual && (flags & F_TAPE)) pl.pair = false;  // the aliased variant has no tape path
   if (pl.pair && bwd && !wide) {
     // pair backward: one 16-byte slot per position doubles as TMA landing zone and output staging
     const bool residual = (flags & F_RESIDUAL) != 0;
@@ -155,8 +155,9 @@ static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, i
       pl.off_work = take(RN * 16);
       pl.off_out = pl.off_work;
       uint64_t ckb = (uint64_t)slots * RN * 8;
-      if (residual && RN * w > ckb) ckb = RN * w;
+      if (!dual && residual && RN * w > ckb) ckb = RN * w;  // (aliased variant: dy shares the checkpoint area)
       pl.off_ckpt = take(ckb ? ckb : 16);
+      if (dual && residual) pl.off_in[0] = pl.off_in[1] = take(RN * w);  // native dy for the final add
       pl.off_red = take((uint64_t)2 * L * (threads / 32) * 4);
       pl.off_w = take((uint64_t)16 * L);
       pl.off_bar = take(32);

@@ -719,8 +719,8 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_bwd_kernel(const RowsParams p
 // ------------------------------------------------------------------------------------------
 // Backward, aliased tile buffer with TWO pairs per thread: half the threads of pair_bwd_kernel for
 // the same tile, so that two CTAs fit one SM with a full register budget (no spills) and one
-// CTA's stage barriers overlap the other's arithmetic.  Plain backward only (from the net output,
-// checkpoints allowed): no replay, no residual, no tape.
+// CTA's stage barriers overlap the other's arithmetic.  Backward from the net output or (F_TAPE) from
+// the stored end state, checkpoints and F_RESIDUAL allowed; no forward replay.
 template <int NG, int ACT, typename T, int MAXT>
 __global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -741,7 +741,10 @@ __global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams
   const T* g_in[4] = {static_cast<const T*>(p.in[0]), static_cast<const T*>(p.in[1]), static_cast<const T*>(p.in[2]),
                       static_cast<const T*>(p.in[3])};
   const float2* ckpt = reinterpret_cast<const float2*>(p.ckpt);
+  T* sdy = reinterpret_cast<T*>(smem + p.off_in[0]);  // F_RESIDUAL: native dy of the tile
   const bool want_rec = p.out[2] != nullptr;
+  const bool residual = (p.flags & F_RESIDUAL) != 0;
+  const bool tape = (p.flags & F_TAPE) != 0;  // the last stage's output state comes from its checkpoint
   const long long BN = p.B * (long long)N;
   const uint32_t n_ck = p.n_ckpt_slots;
 
@@ -759,10 +762,12 @@ __global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams
     const int rows = (int)min((long long)R, p.B - row0);
     const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
     const uint32_t cbytes = (uint32_t)(rows * N * sizeof(float2));
-    mbar_expect_tx(&bar[0], 4 * bytes + n_ck * cbytes);
+    mbar_expect_tx(&bar[0], (tape ? 2 : 4) * bytes + n_ck * cbytes + (residual ? bytes : 0));
 #pragma unroll
-    for (int q = 0; q < 4; ++q) bulk_g2s(win + q * RN, g_in[q] + row0 * N, bytes, &bar[0]);
+    for (int q = 0; q < 4; ++q)
+      if (q >= 2 || !tape) bulk_g2s(win + q * RN, g_in[q] + row0 * N, bytes, &bar[0]);
     for (uint32_t k = 0; k < n_ck; ++k) bulk_g2s(sck + k * RN, ckpt + (long long)k * BN + row0 * N, cbytes, &bar[0]);
+    if (residual) bulk_g2s(sdy, g_in[2] + row0 * N, bytes, &bar[0]);
   };
 
   uint32_t phase = 0;
@@ -816,8 +821,10 @@ __global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams
         for (int pp = 0; pp < PPT; ++pp)
           if (active[pp]) {
             const T* s0 = win + base[pp];
-            ld_native_pair<NG, T>(s0, tt[pp], s, m, X[pp]);
-            ld_native_pair<NG, T>(s0 + RN, tt[pp], s, m, A[pp]);
+            if (!tape) {
+              ld_native_pair<NG, T>(s0, tt[pp], s, m, X[pp]);
+              ld_native_pair<NG, T>(s0 + RN, tt[pp], s, m, A[pp]);
+            }
             ld_native_pair<NG, T>(s0 + 2 * RN, tt[pp], s, m, H[pp]);
             ld_native_pair<NG, T>(s0 + 3 * RN, tt[pp], s, m, G[pp]);
           }
@@ -836,6 +843,8 @@ __global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams
               H[pp][o] = make_float2(va.z, vb.z);
               G[pp][o] = make_float2(va.w, vb.w);
             }
+          }
+          {
             if (rec.ck >= 0) {  // a state saved after stage l replaces the rebuilt one
               const float2* c = sck + rec.ck * RN + base[pp] + tt[pp];
 #pragma unroll
@@ -861,6 +870,12 @@ __global__ void __launch_bounds__(MAXT, 2) pair_bwd_dual_kernel(const RowsParams
 #pragma unroll
         for (int pp = 0; pp < PPT; ++pp)
           if (active[pp]) {
+            if (residual) {
+              float2 gin[NG];
+              ld_native_pair<NG, T>(sdy + base[pp], tt[pp], s, m, gin);
+#pragma unroll
+              for (int o = 0; o < NG; ++o) H[pp][o] = fadd2(H[pp][o], gin[o]);
+            }
             T* wout = win + base[pp];
             st_native_pair<NG, T>(wout, tt[pp], s, m, H[pp]);
             st_native_pair<NG, T>(wout + RN, tt[pp], s, m, G[pp]);
