@@ -255,7 +255,8 @@ def run_b200(args, wl, rank, world, local_rank):
     step_gbs = 10 * w * elems / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
     roofline = {
         "bound": "hbm", "kernel": ("feat_bwd_kernel (ncn_feat.cuh), %d launches per step" % L if per_stage
-                                   else "pair_bwd_wide_kernel (ncn_pairs.cuh)"), "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
+                                   else "pair_bwd_dual_kernel (ncn_pairs.cuh)" if n <= 8 and mode != "recompute" and not (dtype != torch.float32 and mode == "auto")
+                                   else "rows_bwd_kernel / pair_bwd_wide_kernel"), "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
         "unit": "GB/s", "frac": bwd_gbs / peak, "ms_per_launch": bwd_ms / (L if per_stage else 1),
         # measured on the cfg2 shape (fp32, one checkpoint); traffic grows in proportion to the rows
         "traffic": (BWD_TRAFFIC_BYTES_PER_ELEMENT * elems if args.workload in ("cfg2", "small") and mode == "auto" else None),

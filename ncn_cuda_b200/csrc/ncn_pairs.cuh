@@ -328,11 +328,10 @@ __global__ void __launch_bounds__(MAXT, MINB) pair_fwd_kernel(const RowsParams p
 // per position, so four CTAs of half the threads fit one SM: four independent barrier domains
 // whose stage boundaries and copies overlap each other's arithmetic.  With F_RESIDUAL a second
 // native copy of x is kept for the final add.
-template <int NG, int ACT, typename T, int MAXT, int MINB>
+template <int NG, int ACT, typename T, int MAXT, int MINB, int PPT = 2>
 __global__ void __launch_bounds__(MAXT, MINB) pair_fwd_dual_kernel(const RowsParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   using F = ActForm<ACT>;
-  constexpr int PPT = 2;
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int N = p.N, m = p.m, R = p.R, L = p.L;
   const int mh = m >> 1;
