@@ -47,7 +47,7 @@ WORKLOADS = {
 
 # DRAM bytes per element moved by the backward kernel in one launch, from the ncu capture
 # summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over B*N); None until measured.
-BWD_TRAFFIC_BYTES_PER_ELEMENT = 31.27  # profiles/pair_kernels_cfg2_small_ncu_full.md: 1049.2 MB over 33.55 M elements
+BWD_TRAFFIC_BYTES_PER_ELEMENT = 31.39  # profiles/pair_kernels_cfg2_small_ncu_full.md: 1053.2 MB over 33.55 M elements
 
 
 def parse():
