@@ -15,33 +15,33 @@ namespace ncn {
 #endif
 
 template <int LD, int KF, int ACT, typename T>
-static cudaError_t launch_one(const FeatParams& p, int grid, cudaStream_t st, int* occ) {
+static cudaError_t launch_one(const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
   if constexpr (NCN_NC * LD * KF > 1024) {
     return cudaErrorNotSupported;
   } else {
     auto k = NCN_KERNEL<NCN_NC, LD, KF, ACT, T>;
-    if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, kFeatWarps * 32, 0);
-    k<<<grid, kFeatWarps * 32, 0, st>>>(p);
+    if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, 0);
+    k<<<grid, threads, 0, st>>>(p);
     return cudaGetLastError();
   }
 }
 
 template <int LD, int KF>
-static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, int* occ) {
+static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
   if (dtype == DT_F32) {
     switch (act) {
-      case ACT_TANH: return launch_one<LD, KF, ACT_TANH, float>(p, grid, st, occ);
-      case ACT_RELU: return launch_one<LD, KF, ACT_RELU, float>(p, grid, st, occ);
-      case ACT_SIGMOID: return launch_one<LD, KF, ACT_SIGMOID, float>(p, grid, st, occ);
-      case ACT_LINEAR: return launch_one<LD, KF, ACT_LINEAR, float>(p, grid, st, occ);
+      case ACT_TANH: return launch_one<LD, KF, ACT_TANH, float>(p, grid, threads, st, occ);
+      case ACT_RELU: return launch_one<LD, KF, ACT_RELU, float>(p, grid, threads, st, occ);
+      case ACT_SIGMOID: return launch_one<LD, KF, ACT_SIGMOID, float>(p, grid, threads, st, occ);
+      case ACT_LINEAR: return launch_one<LD, KF, ACT_LINEAR, float>(p, grid, threads, st, occ);
       default: return cudaErrorNotSupported;
     }
   }
   switch (act) {  // bf16 storage; the exact tanh (NCN_EXACT_TANH=1) stays with the shared-memory kernels
-    case ACT_TANH_FAST: return launch_one<LD, KF, ACT_TANH_FAST, __nv_bfloat16>(p, grid, st, occ);
-    case ACT_RELU: return launch_one<LD, KF, ACT_RELU, __nv_bfloat16>(p, grid, st, occ);
-    case ACT_SIGMOID: return launch_one<LD, KF, ACT_SIGMOID, __nv_bfloat16>(p, grid, st, occ);
-    case ACT_LINEAR: return launch_one<LD, KF, ACT_LINEAR, __nv_bfloat16>(p, grid, st, occ);
+    case ACT_TANH_FAST: return launch_one<LD, KF, ACT_TANH_FAST, __nv_bfloat16>(p, grid, threads, st, occ);
+    case ACT_RELU: return launch_one<LD, KF, ACT_RELU, __nv_bfloat16>(p, grid, threads, st, occ);
+    case ACT_SIGMOID: return launch_one<LD, KF, ACT_SIGMOID, __nv_bfloat16>(p, grid, threads, st, occ);
+    case ACT_LINEAR: return launch_one<LD, KF, ACT_LINEAR, __nv_bfloat16>(p, grid, threads, st, occ);
     default: return cudaErrorNotSupported;
   }
 }
@@ -54,15 +54,15 @@ static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid,
 #define NCN_FN NCN_CAT(launch_feat_fwd_n, NCN_NC)
 #endif
 
-cudaError_t NCN_FN(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, int* occ) {
+cudaError_t NCN_FN(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
   switch (d) {
-    case 2: return launch_geo<1, 2>(act, dtype, p, grid, st, occ);
-    case 4: return launch_geo<1, 4>(act, dtype, p, grid, st, occ);
-    case 8: return launch_geo<1, 8>(act, dtype, p, grid, st, occ);
-    case 16: return launch_geo<2, 8>(act, dtype, p, grid, st, occ);
-    case 32: return launch_geo<4, 8>(act, dtype, p, grid, st, occ);
-    case 64: return launch_geo<8, 8>(act, dtype, p, grid, st, occ);
-    case 128: return launch_geo<16, 8>(act, dtype, p, grid, st, occ);
+    case 2: return launch_geo<1, 2>(act, dtype, p, grid, threads, st, occ);
+    case 4: return launch_geo<1, 4>(act, dtype, p, grid, threads, st, occ);
+    case 8: return launch_geo<1, 8>(act, dtype, p, grid, threads, st, occ);
+    case 16: return launch_geo<2, 8>(act, dtype, p, grid, threads, st, occ);
+    case 32: return launch_geo<4, 8>(act, dtype, p, grid, threads, st, occ);
+    case 64: return launch_geo<8, 8>(act, dtype, p, grid, threads, st, occ);
+    case 128: return launch_geo<16, 8>(act, dtype, p, grid, threads, st, occ);
     default: return cudaErrorNotSupported;
   }
 }

@@ -413,7 +413,7 @@ static void fill_stage(StageParams& p, int64_t B, int64_t N, int64_t E, int n, i
 }
 
 // ---- register-tiled multi-feature stage kernels (ncn_feat.cuh)
-typedef cudaError_t (*FeatLaunchFn)(int, int, int, const FeatParams&, int, cudaStream_t, int*);
+typedef cudaError_t (*FeatLaunchFn)(int, int, int, const FeatParams&, int, int, cudaStream_t, int*);
 
 static FeatLaunchFn feat_fn(int n, bool bwd) {
   switch (n) {
@@ -459,19 +459,24 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
   p.stride = stage_stride(module_l, p.m);
   p.alpha = (float)alpha;
   p.oma = (float)(1.0 - alpha);
+  // few groups (the reference's own bench has 128): smaller CTAs, so that the warps spread over all SMs
+  const long long want_warps = p.units * C;
+  int wpc = kFeatWarps;
+  while (wpc > 1 && want_warps < (long long)dev.sms * wpc) wpc /= 2;
+  const int threads = wpc * 32;
   int occ = 0;
-  cudaError_t e = fn(d, act, dtype, p, 0, nullptr, &occ);
+  cudaError_t e = fn(d, act, dtype, p, 0, threads, nullptr, &occ);
   if (e == cudaErrorNotSupported) return NCN_ERR_UNSUPPORTED;
   if (e != cudaSuccess) return cuda_fail(e);
   if (occ < 1) return NCN_ERR_UNSUPPORTED;
   if (occ > 32) occ = 32;
   // one warp per (head, unit) at most, a whole number of warps per head
-  long long grid = (p.units * C + kFeatWarps - 1) / kFeatWarps;
+  long long grid = (want_warps + wpc - 1) / wpc;
   if (grid > (long long)dev.sms * occ) grid = (long long)dev.sms * occ;
-  const long long q = C / gcd_ll(C, kFeatWarps);
+  const long long q = C / gcd_ll(C, wpc);
   grid = (grid + q - 1) / q * q;
   if (grid > (long long)dev.sms * 32) return NCN_ERR_UNSUPPORTED;  // more heads than the workspace covers
-  e = fn(d, act, dtype, p, (int)grid, st, nullptr);
+  e = fn(d, act, dtype, p, (int)grid, threads, st, nullptr);
   if (e != cudaSuccess) return cuda_fail(e);
   if (grid_out) *grid_out = (int)grid;
   return NCN_OK;

@@ -9,10 +9,10 @@ namespace ncn {
 struct FeatParams;
 
 #define NCN_DECL(n)                                                                                          \
-  cudaError_t launch_feat_fwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, \
-                                   int* occ);                                                                 \
-  cudaError_t launch_feat_bwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, cudaStream_t st, \
-                                   int* occ);
+  cudaError_t launch_feat_fwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, int threads,     \
+                                   cudaStream_t st, int* occ);                                                                 \
+  cudaError_t launch_feat_bwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, int threads,     \
+                                   cudaStream_t st, int* occ);
 NCN_DECL(2)
 NCN_DECL(4)
 NCN_DECL(8)

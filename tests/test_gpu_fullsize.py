@@ -132,3 +132,32 @@ def test_residual_stack_bf16_slice(ncn):
     assert O.rel_err(y[:rows].float(), ry) < 2e-2 and O.rel_err(ya[:rows].float(), rya) < 2e-2
     assert O.rel_err(x.grad[:rows].float(), rdx) < 2e-2 and O.rel_err(xa.grad[:rows].float(), rdxa) < 2e-2
     assert torch.isfinite(stack.weight.grad).all()
+
+
+def test_multi_feature_stage_full_size(ncn):
+    """The reference's own shape scaled to more than 2^31 elements per tensor (bf16): 64-bit element
+    offsets in the register-tiled kernels, rows independent, a row slice checked against the oracle
+    and the rebuilt stage input against the input that was fed in (fp32 slice)."""
+    dev = torch.device("cuda")
+    B, N, E, C, n, l = 66000, 256, 128, 4, 32, 2   # 2.16e9 elements per tensor
+    g = torch.Generator(device=dev).manual_seed(11)
+    x = torch.randn(B, N, E, device=dev, generator=g, dtype=torch.float32).bfloat16()
+    xa = torch.zeros_like(x)
+    W = (torch.randn(2 * E, generator=torch.Generator().manual_seed(11)) * 0.08).to(dev)
+    y, ya = ncn.ops.stage_fwd(x, xa, W, 0.9, 0, n, C, l)
+    ncn.ops.device_status()
+    # the last rows sit beyond element 2^31
+    lo = B - 40
+    sy, sya = ncn.ops.stage_fwd(x[lo:].clone(), xa[lo:].clone(), W, 0.9, 0, n, C, l)
+    assert torch.equal(sy, y[lo:]) and torch.equal(sya, ya[lo:])
+    ry, rya = O.stage_forward(x[lo:lo + 4].float().cpu(), xa[lo:lo + 4].float().cpu(), W.cpu(), 0.9, "tanh", n, C, l)
+    assert O.rel_err(y[lo:lo + 4].float(), ry) < 2e-2 and O.rel_err(ya[lo:lo + 4].float(), rya) < 2e-2
+    del sy, sya
+    # backward on the same tensors: dx of the last rows equals the slice run alone; dW is additive
+    dy = torch.randn(B, N, E, device=dev, generator=g, dtype=torch.float32).bfloat16()
+    dx, dxa, dW = ncn.ops.stage_bwd(y, ya, dy, xa, W, 0.9, 0, n, C, l)   # dya = 0 (xa is all zeros)
+    ncn.ops.device_status()
+    sdx, sdxa, sdW = ncn.ops.stage_bwd(y[lo:].clone(), ya[lo:].clone(), dy[lo:].clone(), xa[lo:].clone(), W, 0.9, 0, n, C, l)
+    assert torch.equal(sdx, dx[lo:]) and torch.equal(sdxa, dxa[lo:])
+    hdW = ncn.ops.stage_bwd(y[:lo].clone(), ya[:lo].clone(), dy[:lo].clone(), xa[:lo].clone(), W, 0.9, 0, n, C, l)[2]
+    assert O.rel_err(hdW + sdW, dW) < 1e-4
