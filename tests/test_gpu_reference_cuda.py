@@ -47,9 +47,10 @@ def _inputs(seed, B, N=256, E=128):
 
 
 @pytest.mark.parametrize("module_l", [0, 2])
-def test_reference_cuda_forward_agrees(ref, ncn, module_l, capfd):
-    C, n = 4, 32
-    x, xa, W, _, _ = _inputs(module_l, 3)
+@pytest.mark.parametrize("E,C,n", [(128, 4, 32), (32, 2, 16), (16, 2, 8), (12, 3, 4), (2, 1, 2)])  # d = E / C = n
+def test_reference_cuda_forward_agrees(ref, ncn, module_l, E, C, n, capfd):
+    x, xa, W, _, _ = _inputs(module_l, 3, 256, E)
+    W = W * (128 / E) ** 0.5 * 0.5
     xd, xad, Wd = x.cuda(), xa.cuda(), W.cuda()
     ry, rya = ref.forward(xd, xad, Wd, 0.9, 0, n, C, module_l)
     capfd.readouterr()  # the reference prints its shared-memory request on every call
