@@ -39,7 +39,7 @@ def build(reference_root: str) -> str:
         sources=[os.path.join(src, f) for f in ("ncn_cuda.cpp", "ncn_fwd_cuda_kernel.cu", "ncn_bwd_cuda_kernel.cu")],
         extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo"],
         build_directory=OUT,
-        is_python_module=False,  # build only: importing it here would need a GPU-less torch to accept it, which it does, but keep the build side-effect free
+        is_python_module=False,  # build only; load_built() imports the finished file
         verbose=False,
     )
     path = built_path()
@@ -62,4 +62,6 @@ def load_built():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    print(build(sys.argv[1]))

@@ -19,7 +19,6 @@ from oracle.build_ref_cuda import load_built
 
 pytestmark = pytest.mark.gpu
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.fixture(scope="module")
@@ -113,8 +112,8 @@ def test_reference_cuda_backward_and_timing(ref, ncn, capfd):
                 "ours the output allocations and the dW reduction",
     }
     print(json.dumps(record))
-    out = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("NCN_RECORD_DIR")  # optional: keep the record as a file
+    if out and os.path.isdir(out):
         with open(os.path.join(out, "reference_cuda_side_by_side.json"), "w") as f:
             json.dump(record, f, indent=1)
     assert t_our_f < t_ref_f and t_our_b < t_ref_b
