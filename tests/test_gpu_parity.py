@@ -241,6 +241,10 @@ NET_CASES = [
     (100, 96, 4, 7, 0.25, "linear"),  # m = 24, ragged last tile, stride wrap
     (7, 40, 2, 5, 0.3, "relu"),       # m = 20
     (5, 64, 4, 1, 0.3, "sigmoid"),    # single stage through the net call
+    (5, 24, 4, 3, 0.3, "tanh"),       # m = 6: three pairs per row, an odd number of work items per tile
+    (3, 12, 2, 4, 0.3, "tanh"),       # m = 6, n = 2
+    (1, 8, 4, 2, 0.3, "tanh"),        # one row of two groups: a single pair
+    (1030, 256, 8, 3, 0.1, "tanh"),   # several tiles per CTA with a ragged last one
 ]
 
 
