@@ -16,6 +16,27 @@ from . import ops
 from .ncn_pytorch_wrapper_v2 import plan_backward
 
 
+def chunk_bounds(B: int, rows: int):
+    """[begin, end) of the chunks: `rows` rows each, with shorter ones at both ends of a long batch
+    (quarter, quarter, half) so that the first copy in and the last copy out, which nothing
+    overlaps, are short."""
+    if B < 6 * rows or rows < 4:
+        return [(r0, min(B, r0 + rows)) for r0 in range(0, B, rows)]
+    ramp = [rows // 4, rows // 4, rows // 2]
+    sizes = list(ramp)
+    left = B - 2 * sum(ramp)
+    sizes += [rows] * (left // rows)
+    if left % rows:
+        sizes.append(left % rows)
+    sizes += ramp[::-1]
+    out, r0 = [], 0
+    for n in sizes:
+        out.append((r0, r0 + n))
+        r0 += n
+    assert r0 == B
+    return out
+
+
 def net_fwd_bwd_host(
     x: torch.Tensor, xa: torch.Tensor, W: torch.Tensor, dy: torch.Tensor, dya: torch.Tensor,
     alpha: float, activation, n_cache: int, n_head: int,
@@ -46,8 +67,7 @@ def net_fwd_bwd_host(
                  for _ in range(nslot)]
     slot_free = [None] * nslot  # event: kernels of the chunk that used the slot are done
     done_out = []
-    for ci, r0 in enumerate(range(0, B, rows)):
-        r1 = min(B, r0 + rows)
+    for ci, (r0, r1) in enumerate(chunk_bounds(B, rows)):
         k = ci % nslot
         with torch.cuda.stream(s_in):
             if slot_free[k] is not None:
@@ -60,6 +80,8 @@ def net_fwd_bwd_host(
         with torch.cuda.stream(s_k):
             s_k.wait_event(ev_in)
             y, ya, ckpt = ops.net_fwd(bufs[0], bufs[1], Wd, alpha, act, n_cache, n_head, 0, every, False, tape)
+            ev_f = torch.cuda.Event()
+            ev_f.record(s_k)
             if tape:
                 res = ops.net_bwd(None, None, bufs[2], bufs[3], Wd, alpha, act, n_cache, n_head, 0, ckpt=ckpt,
                                   ckpt_every=every, dW_out=dW, tape=True)
@@ -74,8 +96,12 @@ def net_fwd_bwd_host(
             ev_k.record(s_k)
             slot_free[k] = ev_k
         with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_f)  # the outputs leave while the backward still runs
+            for t, h in zip((y, ya), (y_h, ya_h)):
+                t.record_stream(s_out)
+                h[r0:r1].copy_(t, non_blocking=True)
             s_out.wait_event(ev_k)
-            for t, h in zip((y, ya, dx, dxa), (y_h, ya_h, dx_h, dxa_h)):
+            for t, h in zip((dx, dxa), (dx_h, dxa_h)):
                 t.record_stream(s_out)
                 h[r0:r1].copy_(t, non_blocking=True)
             if ckpt is not None:

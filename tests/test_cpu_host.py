@@ -162,3 +162,15 @@ def test_bench_reference_arm_prints_contract_line():
                 "dtype", "data", "config", "cpu_baseline", "e2e"):
         assert key in line, key
     assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port" and line["value"] > 0
+
+
+def test_host_pipeline_chunk_bounds():
+    from ncn_cuda_b200.host import chunk_bounds
+
+    for B, rows in [(65536, 4096), (100, 4096), (30000, 4096), (24576, 4096), (7, 2), (1, 1), (4097, 4096)]:
+        b = chunk_bounds(B, rows)
+        assert b[0][0] == 0 and b[-1][1] == B
+        assert all(x[1] == y[0] for x, y in zip(b, b[1:]))          # contiguous, in order
+        assert all(0 < e - s <= rows for s, e in b)                  # fit the device slots
+    long = chunk_bounds(65536, 4096)
+    assert long[0] == (0, 1024) and long[-1] == (64512, 65536)       # short chunks at both ends
