@@ -281,6 +281,17 @@ struct ActForm<ACT_TANH> {  // tanh T = 1 - 2 / (2^(2 log2e T) + 1) ; 1 - F^2 = 
   static __device__ __forceinline__ float2 gt(float2 g, float2, float2 r) {
     return __fmul2_rn(g, __ffma2_rn(make_float2(-r.x, -r.y), r, r));
   }
+  // The same value with the reciprocal by Newton's iteration on the FMA pipe instead of the
+  // special-function unit (start: exponent/mantissa trick, 12 % off; three steps square that to
+  // below 1e-7).  For kernels that the special-function unit bounds while the FMA pipe idles.
+  static __device__ __forceinline__ float2 r_fma(float2 ts) {
+    const float2 d = __fadd2_rn(make_float2(ex2_approx(ts.x), ex2_approx(ts.y)), f2(1.0f));
+    float2 y = make_float2(__int_as_float(0x7EF311C3 - __float_as_int(d.x)), __int_as_float(0x7EF311C3 - __float_as_int(d.y)));
+    const float2 nd = make_float2(-d.x, -d.y);
+#pragma unroll
+    for (int it = 0; it < 3; ++it) y = __ffma2_rn(y, __ffma2_rn(nd, y, f2(1.0f)), y);  // y += y (1 - d y)
+    return y;
+  }
 };
 template <>
 struct ActForm<ACT_SIGMOID> {  // 1 / (1 + 2^(-log2e T)) ; F' = F (1 - F)

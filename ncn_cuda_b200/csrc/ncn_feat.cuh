@@ -18,6 +18,9 @@
 #pragma once
 #include "ncn_common.cuh"
 
+#ifndef NCN_FEAT_FWD_NEWTON_EVERY
+#define NCN_FEAT_FWD_NEWTON_EVERY 2
+#endif
 #ifndef NCN_FEAT_UNROLL
 #define NCN_FEAT_UNROLL 1
 #endif
@@ -171,7 +174,13 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatPar
 #pragma unroll
           for (int q = 0; q < KP; ++q) {
             const float2 ts = __ffma2_rn(sim, xj[q], __fmul2_rn(X[r][q], alpha_s));
-            const float2 rr = F::r(ts);
+            float2 rr;
+            if constexpr (ACT == ACT_TANH && NCN_FEAT_FWD_NEWTON_EVERY > 0) {
+              // the forward is bound by the special-function unit: some of the reciprocals go to the FMA pipe
+              if ((q % NCN_FEAT_FWD_NEWTON_EVERY) == NCN_FEAT_FWD_NEWTON_EVERY - 1) rr = F::r_fma(ts); else rr = F::r(ts);
+            } else {
+              rr = F::r(ts);
+            }
             A[r][q] = __ffma2_rn(rr, f2(cf1), __ffma2_rn(A[r][q], f2(kM), f2(cf0)));
             X[r][q] = __ffma2_rn(A[r][q], f2(kC), __fmul2_rn(X[r][q], f2(kM)));
           }

@@ -10,6 +10,10 @@
 #pragma once
 #include "ncn_rows.cuh"
 
+#ifndef NCN_FWD_NEWTON_EVERY
+#define NCN_FWD_NEWTON_EVERY 2
+#endif
+
 namespace ncn {
 
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
@@ -43,7 +47,14 @@ struct PFwdSteps {
     }
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
-      const float2 r = F::r(ffma2(X[i], P, Q));
+      float2 r;
+      if constexpr (ACT == ACT_TANH && NCN_FWD_NEWTON_EVERY > 0) {
+        // the forward is bound by the special-function unit while the FMA pipe idles: one position
+        // in NCN_FWD_NEWTON_EVERY takes its reciprocal there
+        if ((i % NCN_FWD_NEWTON_EVERY) == NCN_FWD_NEWTON_EVERY - 1) r = F::r_fma(ffma2(X[i], P, Q)); else r = F::r(ffma2(X[i], P, Q));
+      } else {
+        r = F::r(ffma2(X[i], P, Q));
+      }
       A[i] = ffma2(r, f2(cA), A[i]);
       X[i] = ffma2(A[i], f2(kC), X[i]);
     }
