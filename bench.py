@@ -276,8 +276,10 @@ def run_b200(args, wl, rank, world, local_rank):
         "rows_per_s_per_gpu": value / world,
     }
 
-    if rank == 0 and not args.no_e2e and not layers and not per_stage:
-        line["e2e"] = run_e2e(ncn, wl, dev, dtype, ws, mode, world)
+    if not args.no_e2e and not layers and not per_stage:
+        e2e = run_e2e(ncn, wl, dev, dtype, ws, mode, world, rank)  # every rank: its rows through its own host buffers
+        if rank == 0:
+            line["e2e"] = e2e
     if world > 1:
         dist.barrier()
     if rank == 0 and world == 1 and not args.no_cpu and not layers:
@@ -292,13 +294,17 @@ def run_b200(args, wl, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def run_e2e(ncn, wl, dev, dtype, ws, mode, world):
+def run_e2e(ncn, wl, dev, dtype, ws, mode, world, rank):
     """Same metric through the host-buffer entry: inputs in pinned host memory, results back in
-    pinned host memory, all copies inside the timed region (rank 0's GPU; the other ranks idle)."""
+    pinned host memory, all copies inside the timed region.  Every rank pushes its own rows through
+    its own GPU at the same time; the time is the slowest rank's, the weight gradients are summed
+    over the ranks once per step as in the device-resident run."""
+    import torch.distributed as dist
+
     from ncn_cuda_b200.host import net_fwd_bwd_host
 
     B, N = wl["B"], wl["N"]
-    g = torch.Generator().manual_seed(wl["seed"])
+    g = torch.Generator().manual_seed(wl["seed"] + 1000 * rank)
     hx = torch.empty(B, N, 1, dtype=dtype).pin_memory()
     hx.copy_(torch.randn(B, N, 1, generator=g).to(dtype))
     hxa = torch.zeros(B, N, 1, dtype=dtype).pin_memory()
@@ -308,21 +314,37 @@ def run_e2e(ncn, wl, dev, dtype, ws, mode, world):
     out = tuple(torch.empty(B, N, 1, dtype=dtype).pin_memory() for _ in range(4))
     W = torch.stack([p.detach() for p in ws])
     reps = 2
-    net_fwd_bwd_host(hx, hxa, W, hdy, hdya, 0.9, wl["act"], wl["n"], 1, out=out, backward_mode=mode, device=dev)
+
+    def one():
+        res = net_fwd_bwd_host(hx, hxa, W, hdy, hdya, 0.9, wl["act"], wl["n"], 1, out=out, backward_mode=mode, device=dev)
+        if world > 1:  # the data-parallel exchange: one sum of the flat weight gradient
+            dwd = res[4].to(dev)
+            dist.all_reduce(dwd, op=dist.ReduceOp.SUM)
+            res[4].copy_(dwd)
+
+    one()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        net_fwd_bwd_host(hx, hxa, W, hdy, hdya, 0.9, wl["act"], wl["n"], 1, out=out, backward_mode=mode, device=dev)
+        one()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / reps
     wall = (time.perf_counter() - t0) / reps
+    if world > 1:
+        t = torch.tensor([ms, wall], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, wall = float(t[0].item()), float(t[1].item())
     el = hx.element_size() * B * N
-    return {"value": B / (ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": 4 * el, "d2h_bytes_per_step": 4 * el + W.numel() * 4,
-            "rows": B, "ms_per_step": ms, "wall_ms_per_step": wall * 1e3,
-            "note": "host-buffer call (ncn_cuda_b200.host.net_fwd_bwd_host), chunked 3-stream pipeline, one GPU"}
+    return {"value": world * B / (ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": world * 4 * el,
+            "d2h_bytes_per_step": world * (4 * el + W.numel() * 4), "rows": world * B, "ms_per_step": ms,
+            "wall_ms_per_step": wall * 1e3,
+            "note": "host-buffer call (ncn_cuda_b200.host.net_fwd_bwd_host), chunked 3-stream pipeline on every GPU, max over ranks"}
 
 
 def main():
