@@ -305,13 +305,24 @@ def run_e2e(ncn, wl, dev, dtype, ws, mode, world, rank):
 
     B, N = wl["B"], wl["N"]
     g = torch.Generator().manual_seed(wl["seed"] + 1000 * rank)
-    hx = torch.empty(B, N, 1, dtype=dtype).pin_memory()
-    hx.copy_(torch.randn(B, N, 1, generator=g).to(dtype))
-    hxa = torch.zeros(B, N, 1, dtype=dtype).pin_memory()
-    hdy = torch.empty(B, N, 1, dtype=dtype).pin_memory()
-    hdy.copy_(torch.randn(B, N, 1, generator=g).to(dtype))
-    hdya = torch.zeros(B, N, 1, dtype=dtype).pin_memory()
-    out = tuple(torch.empty(B, N, 1, dtype=dtype).pin_memory() for _ in range(4))
+    ok, err = 1, ""
+    try:  # eight pinned tensors of the full batch per rank; a host that cannot pin them has no e2e number
+        hx = torch.empty(B, N, 1, dtype=dtype).pin_memory()
+        hx.copy_(torch.randn(B, N, 1, generator=g).to(dtype))
+        hxa = torch.zeros(B, N, 1, dtype=dtype).pin_memory()
+        hdy = torch.empty(B, N, 1, dtype=dtype).pin_memory()
+        hdy.copy_(torch.randn(B, N, 1, generator=g).to(dtype))
+        hdya = torch.zeros(B, N, 1, dtype=dtype).pin_memory()
+        out = tuple(torch.empty(B, N, 1, dtype=dtype).pin_memory() for _ in range(4))
+    except RuntimeError as e:
+        ok, err = 0, str(e).splitlines()[0][:200]
+    if world > 1:  # all ranks run it or none does (the repetitions contain a collective)
+        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ok = int(flag.item())
+    if not ok:
+        return {"value": None, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "not measured: pinned host buffers could not be allocated on every rank" + (": " + err if err else "")}
     W = torch.stack([p.detach() for p in ws])
     reps = 3
 
