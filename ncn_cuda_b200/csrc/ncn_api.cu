@@ -4,10 +4,14 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "../../include/ncn_b200.h"
 #include "ncn_generic.cuh"
 #include "ncn_rows_launch.h"
+#include "ncn_lanes_launch.h"
 #include "ncn_feat.cuh"
 #include "ncn_feat_launch.h"
 
@@ -333,6 +337,224 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   return plan_rows_impl(bwd, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, false, pl);
 }
 
+// ---- register-resident row kernels (ncn_lanes.cuh)
+typedef cudaError_t (*LaneLaunchFn)(int, int, const LaneParams&, int, int, size_t, cudaStream_t, int*);
+
+static LaneLaunchFn lane_fn(int n, bool bwd) {
+  switch (n) {
+    case 2: return bwd ? launch_lane_bwd_n2 : launch_lane_fwd_n2;
+    case 4: return bwd ? launch_lane_bwd_n4 : launch_lane_fwd_n4;
+    case 8: return bwd ? launch_lane_bwd_n8 : launch_lane_fwd_n8;
+    default: return nullptr;
+  }
+}
+
+// NCN_LANES=0 switches the family off (A/B measurements); read once.
+static bool lanep_enabled() {  // NCN_LANES_PIPE=0: the plain register-resident backward instead of the pipelined one
+  static const bool on = [] {
+    const char* e = std::getenv("NCN_LANES_PIPE");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+static bool lanes_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("NCN_LANES");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+struct LanePlan {
+  int threads = 0, R = 0, grid = 0, tpr = 0, ea_max = 0, occ = 0;
+  size_t smem = 0;
+  uint32_t off_work = 0, off_res = 0, off_ckpt = 0, off_halo = 0, off_red = 0, off_w = 0, off_bar = 0;
+  uint32_t halo_warp_bytes = 0, n_ckpt_slots = 0;
+  int pipelined = 0;
+  long long tiles = 0;
+};
+
+static int lane_ilog2(long long v) {
+  int e = 0;
+  while ((1LL << (e + 1)) <= v) ++e;
+  return e;
+}
+
+// The family covers: one feature per position, n in {2,4,8}, m = N/n a power of two with a whole
+// number of warps per row and at most one CTA of threads per row, and stage strides that do not
+// wrap (2^(l-1) < m for every stage), so that every change of stride is a shift by a power of two.
+static bool lane_shape_ok(int64_t N, int64_t E, int n, int C, int l0, int L, int dtype, int* e_needed_max) {
+  if (E != 1 || C != 1 || lane_fn(n, false) == nullptr) return false;
+  if (N % n != 0) return false;
+  const int64_t m = N / n;
+  if (m <= 0 || (m & (m - 1)) != 0) return false;
+  const int G = lane_groups(n);
+  if (m % (32 * G) != 0 || m / G > kLaneThreads) return false;
+  const int64_t quantum = dtype == DT_BF16 ? 8 : 4;
+  if (N % quantum != 0) return false;
+  const int last = l0 + L - 1;
+  if (last >= 1 && (last - 1) >= lane_ilog2(m)) return false;  // 2^(last-1) >= m: the stride wraps
+  // largest shift: back from the last stride to 0 (2^(last-1)), or the first one up to stride(l0)
+  int emax = -1;
+  if (last >= 1) emax = last - 1;
+  *e_needed_max = emax;
+  return true;
+}
+
+// Lay one CTA out.  ea: shifts of up to 2^ea blocks go by shuffles + halo, longer ones through the
+// tile buffer (which must then hold fp32 values).
+static bool lane_layout(bool bwd, int N, int n, int L, int dtype, int flags, int n_ck, int R, int tpr, int ea, int e_need,
+                        uint32_t limit, LanePlan& pl) {
+  const int w = dtype == DT_BF16 ? 2 : 4;
+  const int NS = bwd ? 4 : 2;
+  const bool residual = (flags & F_RESIDUAL) != 0;
+  const bool long_shifts = e_need > ea;
+  const uint64_t RN = (uint64_t)R * N;
+  const int threads = R * tpr;
+  const int warps = threads / 32;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { uint64_t o = off; off = (off + bytes + 127) / 128 * 128; return (uint32_t)o; };
+  pl.off_work = take(NS * RN * (long_shifts ? 4 : w));
+  pl.off_res = residual ? take(RN * w) : pl.off_work;
+  pl.off_ckpt = take(n_ck ? (uint64_t)n_ck * RN * 8 : 16);
+  pl.halo_warp_bytes = ea >= 0 ? (uint32_t)(NS * lane_halo_floats(n, ea) * 4) : 0;
+  pl.halo_warp_bytes = (pl.halo_warp_bytes + 15u) / 16u * 16u;
+  pl.off_halo = take((uint64_t)2 * warps * pl.halo_warp_bytes + 16);
+  pl.off_red = take(bwd ? (uint64_t)2 * L * warps * 4 : 16);
+  pl.off_w = take((uint64_t)16 * L);
+  pl.off_bar = take(32);
+  if (off > limit) return false;
+  pl.threads = threads; pl.R = R; pl.tpr = tpr; pl.ea_max = ea; pl.smem = (size_t)off;
+  pl.n_ckpt_slots = (uint32_t)n_ck;
+  return true;
+}
+
+// Pipelined backward (n = 4, ncn_lanes_pipe.cuh): a thread runs the two halves of its row half a
+// stage apart; every shift goes by shuffles + halo, and the halo lives in the tile buffer.  Needs
+// every change of stride to stay within a warp's reach: 3 * 2^e / 2 <= 24 lanes, i.e. e <= 4.
+static bool lanep_layout(int N, int L, int dtype, int flags, int n_ck, int R, int tpr, int e_need, uint32_t limit,
+                         LanePlan& pl) {
+  if (e_need > 4) return false;
+  const int w = dtype == DT_BF16 ? 2 : 4;
+  const bool residual = (flags & F_RESIDUAL) != 0;
+  const uint64_t RN = (uint64_t)R * N;
+  const int threads = R * tpr;
+  const int warps = threads / 32;
+  const int kmax = 3 * (e_need >= 0 ? (1 << e_need) : 0);
+  const uint32_t so = (uint32_t)((4 * (kmax + 2) + 7) / 8 * 8);  // bytes per (stream, offset) region
+  pl.halo_warp_bytes = 4 * 3 * so;
+  uint64_t work = 4 * RN * w;
+  const uint64_t halo = (uint64_t)2 * warps * pl.halo_warp_bytes;  // two half-row "warps" per warp
+  if (halo > work) work = halo;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { uint64_t o = off; off = (off + bytes + 127) / 128 * 128; return (uint32_t)o; };
+  pl.off_work = take(work);
+  pl.off_halo = pl.off_work;
+  pl.off_res = residual ? take(RN * w) : pl.off_work;
+  pl.off_ckpt = take(n_ck ? (uint64_t)n_ck * RN * 8 : 16);
+  pl.off_red = take((uint64_t)2 * L * warps * 4);
+  pl.off_w = take((uint64_t)16 * L);
+  pl.off_bar = take(32);
+  if (off > limit) return false;
+  pl.threads = threads; pl.R = R; pl.tpr = tpr; pl.ea_max = 4; pl.smem = (size_t)off;
+  pl.n_ckpt_slots = (uint32_t)n_ck;
+  pl.pipelined = 1;
+  return true;
+}
+
+struct LaneKey {
+  int dev, bwd, N, n, L, l0, dtype, flags, n_ck, act;
+  long long B;
+  bool operator==(const LaneKey& o) const {
+    return dev == o.dev && bwd == o.bwd && N == o.N && n == o.n && L == o.L && l0 == o.l0 && dtype == o.dtype &&
+           flags == o.flags && n_ck == o.n_ck && act == o.act && B == o.B;
+  }
+};
+
+// NCN_OK with pl filled, NCN_ERR_UNSUPPORTED when the family does not cover the arguments.
+// Plans are remembered per argument set: a plan costs a few occupancy queries.
+static int plan_lanes(bool bwd, int64_t B, int64_t N, int64_t E, int n, int C, int l0, int L, int dtype, int flags,
+                      int n_ck, const DevInfo& dev, int act, LanePlan& pl) {
+  if (!lanes_enabled()) return NCN_ERR_UNSUPPORTED;
+  if (flags & F_RECOMPUTE) return NCN_ERR_UNSUPPORTED;
+  int e_need = -1;
+  if (!lane_shape_ok(N, E, n, C, l0, L, dtype, &e_need)) return NCN_ERR_UNSUPPORTED;
+  static std::mutex mu;
+  static std::vector<std::pair<LaneKey, std::pair<int, LanePlan>>> cache;
+  const LaneKey key{dev.dev, bwd ? 1 : 0, (int)N, n, L, l0, dtype, flags & (F_RESIDUAL | F_TAPE), n_ck, act, (long long)B};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (auto& kv : cache)
+      if (kv.first == key) {
+        pl = kv.second.second;
+        return kv.second.first;
+      }
+  }
+  const int G = lane_groups(n);
+  const int tpr = (int)(N / n) / G;
+  int R = kLaneThreads / tpr;
+  if ((int64_t)R > B) R = (int)B;
+  if (R < 1) R = 1;
+  const int want_occ = bwd ? kLaneBwdBlocks : kLaneFwdBlocks;
+  const int cap = lane_ea_cap(n);
+  int ea_hi = e_need < cap ? e_need : cap;
+  int ea_lo = lane_ilog2(G) - 1;  // longer shifts through the tile buffer must be multiples of G blocks
+  if (ea_lo > ea_hi) ea_lo = ea_hi;
+  int rc = NCN_ERR_UNSUPPORTED;
+  LanePlan best;
+  bool have_pipe = false;
+  if (bwd && n == 4 && lanep_enabled()) {
+    LanePlan trial;
+    if (lanep_layout((int)N, L, dtype, flags, n_ck, R, tpr, e_need, (uint32_t)dev.smem_optin, trial)) {
+      int occ = 0;
+      LaneParams dummy{};
+      dummy.pipelined = 1;
+      cudaError_t e = lane_fn(n, true)(act, dtype, dummy, 0, trial.threads, trial.smem, nullptr, &occ);
+      if (e != cudaSuccess) return cuda_fail(e);
+      if (occ >= 1) {
+        trial.occ = occ > want_occ ? want_occ : occ;
+        best = trial;
+        rc = NCN_OK;
+        have_pipe = true;
+      }
+    }
+  }
+  for (int ea = ea_hi; !have_pipe && ea >= ea_lo; --ea) {
+    LanePlan trial;
+    if (!lane_layout(bwd, (int)N, n, L, dtype, flags, n_ck, R, tpr, ea, e_need, (uint32_t)dev.smem_optin, trial)) continue;
+    int occ = 0;
+    LaneParams dummy{};
+    cudaError_t e = lane_fn(n, bwd)(act, dtype, dummy, 0, trial.threads, trial.smem, nullptr, &occ);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (occ < 1) continue;
+    if (occ > want_occ) occ = want_occ;
+    trial.occ = occ;
+    if (rc != NCN_OK || occ > best.occ) { best = trial; rc = NCN_OK; }
+    if (occ >= want_occ) break;
+  }
+  if (rc == NCN_OK) {
+    best.tiles = (B + best.R - 1) / best.R;
+    long long grid = (long long)dev.sms * best.occ;
+    if (grid > best.tiles) grid = best.tiles;
+    best.grid = (int)grid;
+    pl = best;
+  }
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() >= 64) cache.erase(cache.begin());
+    cache.emplace_back(key, std::make_pair(rc, pl));
+  }
+  return rc;
+}
+
+static void fill_lane(LaneParams& p, const LanePlan& pl) {
+  p.R = pl.R; p.tpr = pl.tpr; p.ea_max = pl.ea_max; p.tiles = pl.tiles;
+  p.off_work = pl.off_work; p.off_res = pl.off_res; p.off_ckpt = pl.off_ckpt; p.off_halo = pl.off_halo;
+  p.off_red = pl.off_red; p.off_w = pl.off_w; p.off_bar = pl.off_bar;
+  p.halo_warp_bytes = pl.halo_warp_bytes; p.n_ckpt_slots = pl.n_ckpt_slots;
+  p.pipelined = pl.pipelined;
+}
+
 static void fill_offsets(RowsParams& p, const Plan& pl) {
   p.off_in[0] = pl.off_in[0];
   p.off_in[1] = pl.off_in[1];
@@ -551,6 +773,13 @@ int ncn_net_supported(int64_t B, int64_t N, int64_t E, int n_cache, int n_head, 
   Plan pl;
   if ((flags & F_TAPE) && (flags & F_RECOMPUTE)) return 0;
   const int n_ck = (flags & F_RECOMPUTE) ? 0 : ckpt_slots(L, ckpt_every, flags);
+  {
+    LanePlan lf, lb;
+    const int act = fused_act(ACT_TANH, dtype);
+    if (plan_lanes(false, B, N, E, n_cache, n_head, 0, L, dtype, flags, 0, dev, act, lf) == NCN_OK &&
+        plan_lanes(true, B, N, E, n_cache, n_head, 0, L, dtype, flags, n_ck, dev, act, lb) == NCN_OK)
+      return 1;
+  }
   if (plan_rows(false, B, (int)N, n_cache, L, dtype, flags, 0, false, dev, ACT_TANH, pl) != NCN_OK) return 0;
   if (plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, false, dev, ACT_TANH, pl) != NCN_OK) return 0;
   return 1;
@@ -570,12 +799,38 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
   DevInfo dev;
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
   const int act = fused_act(map_act(activation), dtype);
+  float* ck_used = (ckpt && ckpt_slots(L, ckpt_every, flags) > 0) ? ckpt : nullptr;
+  {
+    // register-resident family; its stored states have their own order, so with states it is used
+    // only where the backward of the same arguments is of this family too
+    LanePlan lp, lb;
+    const int n_ck = ck_used ? ckpt_slots(L, ckpt_every, flags) : 0;
+    bool lanes = plan_lanes(false, B, N, E, n_cache, n_head, first_module, L, dtype, flags, 0, dev, act, lp) == NCN_OK;
+    if (lanes && n_ck > 0)
+      lanes = plan_lanes(true, B, N, E, n_cache, n_head, first_module, L, dtype, flags, n_ck, dev, act, lb) == NCN_OK;
+    if (lanes) {
+      LaneParams q{};
+      q.in[0] = x; q.in[1] = xa;
+      q.out[0] = y; q.out[1] = ya;
+      q.ckpt = ck_used;
+      q.ckpt_every = ckpt_every;
+      q.W = W;
+      q.status = dev.status;
+      q.B = B; q.N = (int)N; q.m = (int)(N / n_cache); q.L = L; q.l0 = first_module;
+      q.flags = flags & (F_RESIDUAL | F_TAPE);
+      q.alpha = (float)alpha;
+      q.oma = (float)(1.0 - alpha);
+      fill_lane(q, lp);
+      cudaError_t e = lane_fn(n_cache, false)(act, dtype, q, lp.grid, lp.threads, lp.smem, (cudaStream_t)stream, nullptr);
+      return e == cudaSuccess ? NCN_OK : cuda_fail(e);
+    }
+  }
   Plan pl;
   if ((rc = plan_rows(false, B, (int)N, n_cache, L, dtype, flags, 0, false, dev, act, pl)) != NCN_OK) return rc;
   RowsParams p{};
   p.in[0] = x; p.in[1] = xa;
   p.out[0] = y; p.out[1] = ya;
-  p.ckpt = (ckpt && ckpt_slots(L, ckpt_every, flags) > 0) ? ckpt : nullptr;
+  p.ckpt = ck_used;
   p.ckpt_every = ckpt_every;
   p.W = W;
   p.status = dev.status;
@@ -589,10 +844,14 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
   return e == cudaSuccess ? NCN_OK : cuda_fail(e);
 }
 
-int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
-                void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, void* workspace,
-                size_t workspace_bytes, int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module,
-                int L, double alpha, int activation, int dtype, int flags, int dw_accumulate, void* stream) {
+// Backward of a net, shared by ncn_net_bwd and ncn_net_bwd_noalloc: `partials` is the scratch for the
+// per-CTA weight-gradient sums (capacity_floats of it); a launch that needs more returns short_err.
+static int net_bwd_impl(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx,
+                        void* dxa, void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every,
+                        float* partials, size_t capacity_floats, bool full_workspace, int short_err, int64_t B,
+                        int64_t N, int64_t E,
+                        int n_cache, int n_head, int first_module, int L, double alpha, int activation, int dtype,
+                        int flags, int dw_accumulate, void* stream) {
   int rc = check_common(B, N, E, n_cache, n_head, dtype);
   if (rc != NCN_OK) return rc;
   if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
@@ -607,20 +866,48 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
     return NCN_ERR_ALIGN;
   DevInfo dev;
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
-  if (!workspace || workspace_bytes < workspace_floats(dev, E, L) * sizeof(float)) return NCN_ERR_WORKSPACE;
+  if (!partials || (full_workspace && capacity_floats < workspace_floats(dev, E, L))) return short_err;
   const int act = fused_act(map_act(activation), dtype);
   const bool use_ck = ckpt && !(flags & F_RECOMPUTE) && ckpt_slots(L, ckpt_every, flags) > 0;
   const int n_ck = use_ck ? ckpt_slots(L, ckpt_every, flags) : 0;
+  {
+    // register-resident family (with stored states: only where the forward is of this family too)
+    LanePlan lp, lf;
+    bool lanes = plan_lanes(true, B, N, E, n_cache, n_head, first_module, L, dtype, flags, n_ck, dev, act, lp) == NCN_OK;
+    if (lanes && n_ck > 0)
+      lanes = plan_lanes(false, B, N, E, n_cache, n_head, first_module, L, dtype, flags, 0, dev, act, lf) == NCN_OK;
+    if (lanes) {
+      if ((size_t)lp.grid * 2 * (size_t)L > capacity_floats) return short_err;
+      LaneParams q{};
+      q.in[0] = s0; q.in[1] = s1; q.in[2] = dy; q.in[3] = dya;
+      q.out[0] = dx; q.out[1] = dxa; q.out[2] = x_rec; q.out[3] = xa_rec;
+      q.ckpt = use_ck ? const_cast<float*>(ckpt) : nullptr;
+      q.ckpt_every = ckpt_every;
+      q.W = W;
+      q.partials = partials;
+      q.status = dev.status;
+      q.B = B; q.N = (int)N; q.m = (int)(N / n_cache); q.L = L; q.l0 = first_module;
+      q.flags = flags & (F_RESIDUAL | F_TAPE);
+      q.alpha = (float)alpha;
+      q.oma = (float)(1.0 - alpha);
+      fill_lane(q, lp);
+      cudaError_t e = lane_fn(n_cache, true)(act, dtype, q, lp.grid, lp.threads, lp.smem, (cudaStream_t)stream, nullptr);
+      if (e != cudaSuccess) return cuda_fail(e);
+      return reduce_dw(partials, dW, lp.grid, 2 * L, dw_accumulate, (cudaStream_t)stream);
+    }
+  }
   Plan pl;
   if ((rc = plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, x_rec != nullptr, dev, act, pl)) != NCN_OK)
     return rc;
+  // one row of 2L partial sums per CTA
+  if ((size_t)pl.grid * 2 * (size_t)L > capacity_floats) return short_err;
   RowsParams p{};
   p.in[0] = s0; p.in[1] = s1; p.in[2] = dy; p.in[3] = dya;
   p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
   p.ckpt = use_ck ? const_cast<float*>(ckpt) : nullptr;
   p.ckpt_every = ckpt_every;
   p.W = W;
-  p.partials = static_cast<float*>(workspace);
+  p.partials = partials;  // every element the reduction reads is written by the kernel first
   p.status = dev.status;
   p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
   p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE | F_TAPE)) | (pl.red_thread ? F_RED_THREAD : 0);
@@ -631,6 +918,15 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
                                                                              (cudaStream_t)stream, nullptr);
   if (e != cudaSuccess) return cuda_fail(e);
   return reduce_dw(p.partials, dW, pl.grid, 2 * L, dw_accumulate, (cudaStream_t)stream);
+}
+
+int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
+                void* x_rec, void* xa_rec, float* dW, const float* ckpt, int ckpt_every, void* workspace,
+                size_t workspace_bytes, int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int first_module,
+                int L, double alpha, int activation, int dtype, int flags, int dw_accumulate, void* stream) {
+  return net_bwd_impl(s0, s1, dy, dya, W, dx, dxa, x_rec, xa_rec, dW, ckpt, ckpt_every, static_cast<float*>(workspace),
+                      workspace_bytes / sizeof(float), true, NCN_ERR_WORKSPACE, B, N, E, n_cache, n_head, first_module, L,
+                      alpha, activation, dtype, flags, dw_accumulate, stream);
 }
 
 int ncn_stage_fwd(const void* x, const void* xa, const float* W, void* y, void* ya, int64_t B, int64_t N, int64_t E,
@@ -765,46 +1061,11 @@ extern "C" int ncn_net_bwd_noalloc(const void* s0, const void* s1, const void* d
                                    int ckpt_every, int64_t B, int64_t N, int64_t E, int n_cache, int n_head,
                                    int first_module, int L, double alpha, int activation, int dtype, int flags,
                                    int dw_accumulate, void* stream) {
-  int rc = check_common(B, N, E, n_cache, n_head, dtype);
-  if (rc != NCN_OK) return rc;
-  if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
-  const bool tape = (flags & F_TAPE) != 0;  // the state after the last stage comes from ckpt; s0, s1 unused
-  if (tape && (flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
-  if ((!tape && (!s0 || !s1)) || (tape && !ckpt) || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
-  if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
-  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
-  if ((flags & F_RESIDUAL) && !(flags & (F_RECOMPUTE | F_TAPE))) return NCN_ERR_UNSUPPORTED;
-  if (!aligned16(s0) || !aligned16(s1) || !aligned16(dy) || !aligned16(dya) || !aligned16(dx) || !aligned16(dxa) ||
-      (x_rec && (!aligned16(x_rec) || !aligned16(xa_rec))) || (ckpt && !aligned16(ckpt)))
-    return NCN_ERR_ALIGN;
-  DevInfo dev;
-  if ((rc = get_dev(dev)) != NCN_OK) return rc;
   float* scratch = nullptr;
-  if ((rc = noalloc_scratch(&scratch)) != NCN_OK) return rc;
-  const int act = fused_act(map_act(activation), dtype);
-  const bool use_ck = ckpt && !(flags & F_RECOMPUTE) && ckpt_slots(L, ckpt_every, flags) > 0;
-  const int n_ck = use_ck ? ckpt_slots(L, ckpt_every, flags) : 0;
-  Plan pl;
-  if ((rc = plan_rows(true, B, (int)N, n_cache, L, dtype, flags, n_ck, x_rec != nullptr, dev, act, pl)) != NCN_OK)
-    return rc;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != NCN_OK) return rc;
   // one row of 2L partial sums per CTA must fit the fixed array
-  if ((size_t)pl.grid * 2 * (size_t)L > kNoAllocFloats) return NCN_ERR_TOO_LARGE;
-  RowsParams p{};
-  p.in[0] = s0; p.in[1] = s1; p.in[2] = dy; p.in[3] = dya;
-  p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
-  p.ckpt = use_ck ? const_cast<float*>(ckpt) : nullptr;
-  p.ckpt_every = ckpt_every;
-  p.W = W;
-  p.partials = scratch;  // every element the reduction reads is written by the kernel first
-  p.status = dev.status;
-  p.B = B; p.N = (int)N; p.m = (int)(N / n_cache); p.L = L; p.l0 = first_module;
-  p.flags = (flags & (F_RESIDUAL | F_RECOMPUTE | F_TAPE)) | (pl.red_thread ? F_RED_THREAD : 0);
-  p.alpha = (float)alpha;
-  p.oma = (float)(1.0 - alpha);
-  fill_offsets(p, pl);
-  cudaError_t e = (pl.pair ? pair_fn(n_cache, true) : rows_fn(n_cache, true))(act, dtype, p, pl.grid, pl.threads, pl.smem,
-                                                                             (cudaStream_t)stream, nullptr);
-  if (e != cudaSuccess) return cuda_fail(e);
-  return reduce_dw(p.partials, dW, pl.grid, 2 * L, dw_accumulate, (cudaStream_t)stream);
+  return net_bwd_impl(s0, s1, dy, dya, W, dx, dxa, x_rec, xa_rec, dW, ckpt, ckpt_every, scratch, kNoAllocFloats,
+                      false, NCN_ERR_TOO_LARGE, B, N, E, n_cache, n_head, first_module, L, alpha, activation, dtype, flags,
+                      dw_accumulate, stream);
 }
-

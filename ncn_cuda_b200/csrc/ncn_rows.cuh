@@ -96,16 +96,20 @@ __device__ __forceinline__ void group_addrs(uint32_t row_addr, int g, int s, int
 // Stage table: scaled weights, stride s = 0 for stage 0 else 2^(stage-1) mod m
 // (torch_ref/ncn_pytorch.py:38), and the checkpoint index (a state is kept after every
 // ckpt_every-th stage except the last; with F_TAPE the last stage's state takes the slot after those).
-__device__ __forceinline__ void fill_stage_table(StageRec* rec, const RowsParams& p, bool have_ckpt, int tid, int nthr) {
-  for (int i = tid; i < p.L; i += nthr) {
+__device__ __forceinline__ void fill_stage_table(StageRec* rec, const float* W, float oma, int l0, int m, int L,
+                                                 int ckpt_every, int flags, bool have_ckpt, int tid, int nthr) {
+  for (int i = tid; i < L; i += nthr) {
     StageRec r;
-    r.owi = p.W[2 * i] * p.oma;
-    r.owj = p.W[2 * i + 1] * p.oma;
-    r.s = stage_stride(p.l0 + i, p.m);
-    r.ck = (have_ckpt && p.ckpt_every > 0 && i != p.L - 1 && ((i + 1) % p.ckpt_every == 0)) ? (i + 1) / p.ckpt_every - 1 : -1;
-    if (have_ckpt && (p.flags & F_TAPE) && i == p.L - 1) r.ck = p.ckpt_every > 0 ? (p.L - 1) / p.ckpt_every : 0;
+    r.owi = W[2 * i] * oma;
+    r.owj = W[2 * i + 1] * oma;
+    r.s = stage_stride(l0 + i, m);
+    r.ck = (have_ckpt && ckpt_every > 0 && i != L - 1 && ((i + 1) % ckpt_every == 0)) ? (i + 1) / ckpt_every - 1 : -1;
+    if (have_ckpt && (flags & F_TAPE) && i == L - 1) r.ck = ckpt_every > 0 ? (L - 1) / ckpt_every : 0;
     rec[i] = r;
   }
+}
+__device__ __forceinline__ void fill_stage_table(StageRec* rec, const RowsParams& p, bool have_ckpt, int tid, int nthr) {
+  fill_stage_table(rec, p.W, p.oma, p.l0, p.m, p.L, p.ckpt_every, p.flags, have_ckpt, tid, nthr);
 }
 
 template <int NG, int ACT, typename T, int MAXT>
