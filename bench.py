@@ -7,8 +7,12 @@ N > 1, the NCCL sum of dW) over one batch of synthetic rows.  With N > 1 (launch
 one rank per GPU) every rank runs the same per-GPU workload on its own rows (weak scaling) and
 `value` is the whole-job rows/s from the slowest rank's device time.
 
+A default run (workload cfg2) then measures the other configurations for a few steps each and
+attaches them under "workloads" (one GPU: configs 2-linear, 4, 3, 5, 1; several GPUs: config 5).
+
 `--impl reference` times the CPU restatement of the reference's torch_ref path (oracle/) on the
-host cores instead; rank 0 only.
+host cores instead, rank 0 only, and beside it the reference's own literal torch_ref loops where
+oracle/_ref/ holds them.
 """
 from __future__ import annotations
 
@@ -27,6 +31,8 @@ import torch  # noqa: E402
 
 # name -> per-GPU shape.  cfg2 is the configuration the headline metric is quoted on.
 WORKLOADS = {
+    "cfg1": dict(B=1024, N=1024, n=2, L=10, w_var=0.5, dtype="f32", act="tanh", seed=0,
+                 desc="CPU-sized NCN layer fp32 x[1024,1024] g=2 10 stages tanh"),
     "cfg2": dict(B=65536, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="tanh", seed=1,
                  desc="single-GPU NCN layer fp32 x[65536,4096] g=4 6 stages tanh"),
     "cfg2_linear": dict(B=65536, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="linear", seed=1,
@@ -45,9 +51,20 @@ WORKLOADS = {
                   desc="cfg2 with 8192 rows (profiling case)"),
 }
 
-# DRAM bytes per element moved by the backward kernel in one launch, from the ncu capture
-# summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over B*N); None until measured.
-BWD_TRAFFIC_BYTES_PER_ELEMENT = 31.39  # profiles/pair_kernels_cfg2_small_ncu_full.md: 1053.2 MB over 33.55 M elements
+# Workloads measured for a few steps after the headline one in a default run (one GPU: all of them;
+# several GPUs: the stack, which is the configuration quoted at 1/2/4/8 GPUs).
+EXTRA_1GPU = ["cfg2_linear", "cfg4", "cfg3", "cfg5", "cfg1"]
+EXTRA_NGPU = ["cfg5"]
+
+# DRAM bytes per element moved by the backward kernel in one launch (dram__bytes_read.sum +
+# dram__bytes_write.sum over B*N) from an ncu capture of the 8192-row case of cfg2 (fp32, one stored
+# state): 1056.2 MB over 33.55 M elements.  Traffic grows in proportion to the rows, so the full
+# launch is this figure times its elements.
+BWD_TRAFFIC_BYTES_PER_ELEMENT = 31.48
+
+# rows per step of the CPU arms (both the cpu_baseline leg and --impl reference use this one rule)
+CPU_ROWS_PER_STEP = 1024
+CPU_STEPS = 5
 
 
 def parse():
@@ -60,7 +77,8 @@ def parse():
     ap.add_argument("--mode", default=None, help="backward mode override: auto|checkpoint|invert|recompute|tape")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-extra", action="store_true", help="skip the other workloads after the headline one")
+    ap.add_argument("--extra-steps", type=int, default=5)
     return ap.parse_args()
 
 
@@ -116,73 +134,109 @@ class ClockSampler:
                 "samples": len(s)}
 
 
-# ------------------------------------------------------------------ CPU arm (oracle)
-def cpu_rows_per_s(wl, seconds, threads=None, rows=None):
-    """Vectorised torch-CPU restatement of the reference's torch_ref path, forward + autograd
-    backward, on a bounded sample of the workload's rows."""
+# ------------------------------------------------------------------ CPU arms
+def config_of(wl, mode=None, world=1):
+    """The `config` object of a JSON line: the same keys in the GPU arm and in the reference arm."""
+    w = 4 if wl["dtype"] == "f32" else 2
+    return {"workload": wl["desc"], "rows_per_gpu": wl["B"], "D": wl["N"], "E": wl.get("E", 1), "heads": wl.get("C", 1),
+            "g": wl["n"], "stages": wl["L"], "layers": wl.get("layers", 1), "activation": wl["act"],
+            "backward_mode": mode or wl.get("mode", "auto"), "parallelism": f"dp{world}",
+            "l2": "inputs larger than L2 (%.2f GB per tensor)" % (wl["B"] * wl["N"] * wl.get("E", 1) * w / 1e9)}
+
+
+def cpu_port_rows_per_s(wl, steps=CPU_STEPS, warmup=1, rows=CPU_ROWS_PER_STEP, threads=None):
+    """The oracle (vectorised torch-CPU restatement of the reference's torch_ref path), forward +
+    autograd backward, on `rows` rows of the workload per step; median over `steps` timed steps.
+    One sampling rule for every CPU figure this file prints."""
     from oracle import ncn_oracle as O
 
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
-    fixed = rows is not None
-    if not fixed:  # first call: spin up the thread pool and autograd before anything is timed
-        xw, xaw, wsw, dyw, dyaw = O.make_inputs(wl["seed"], 4, wl["N"], wl.get("E", 1), wl["L"], wl["w_var"])
-        O.net_fwd_bwd(xw, xaw, wsw, dyw, dyaw, 0.9, wl["act"], wl["n"], wl.get("C", 1))
-    rows = rows or 8
-    dt_run = 0.0
-    while True:
-        x, xa, ws, dy, dya = O.make_inputs(wl["seed"], rows, wl["N"], wl.get("E", 1), wl["L"], wl["w_var"])
+    rows = min(rows, wl["B"])
+    E, C = wl.get("E", 1), wl.get("C", 1)
+    x, xa, ws, dy, dya = O.make_inputs(wl["seed"], rows, wl["N"], E, wl["L"], wl["w_var"])
+    times = []
+    for i in range(warmup + steps):
         t0 = time.perf_counter()
-        O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, wl["act"], wl["n"], wl.get("C", 1))
-        dt_run = time.perf_counter() - t0
-        if fixed or dt_run >= seconds / 3 or rows >= wl["B"] or rows >= 4096:
-            break
-        rows = min(wl["B"], max(rows * 2, int(rows * (seconds / 2) / max(dt_run, 1e-3))))
-    return rows / dt_run, threads, rows, dt_run
+        O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, wl["act"], wl["n"], C)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    med = sorted(times)[len(times) // 2]
+    ws_mb = 5 * rows * wl["N"] * E * 4 / 1e6
+    sample = (f"{rows} of {wl['B']} rows of the workload per step ({ws_mb:.0f} MB of fp32 tensors), median of {len(times)} steps "
+              f"after {warmup} warm-up, vectorised torch-CPU restatement of torch_ref, forward + autograd backward")
+    return {"value": rows / med, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample}, med, times
+
+
+def cpu_literal_rows_per_s(rows=2):
+    """The reference's OWN torch_ref loops (RefTorchNaive, torch_ref/ncn_pytorch.py:103-124; one Python
+    iteration per batch row, head, group and step), forward + autograd backward on `rows` rows of
+    config 1.  Present only where oracle/build_ref_python.py has put the reference's files under
+    oracle/_ref/; returns None otherwise."""
+    from oracle import build_ref_python
+    from oracle import ncn_oracle as O
+
+    mod = build_ref_python.load("torch_ref.ncn_pytorch")
+    if mod is None:
+        return None
+    wl = WORKLOADS["cfg1"]
+    x, xa, ws, dy, dya = O.make_inputs(wl["seed"], rows, wl["N"], 1, wl["L"], wl["w_var"])
+    x.requires_grad_(True)
+    xa.requires_grad_(True)
+    ws = [w.requires_grad_(True) for w in ws]
+    net = mod.RefTorchNaive(0.9, "tanh", wl["L"], wl["n"], 1, ws)
+    t0 = time.perf_counter()
+    y, ya = net(x, xa)
+    y.backward(dy)
+    dt = time.perf_counter() - t0
+    return {"value": rows / dt, "unit": "rows/s", "cores": 1, "kind": "reference",
+            "sample": f"{rows} rows of config 1 (x[1024,1024], g=2, 10 stages), the reference's literal RefTorchNaive loops "
+                      f"(interpreter-bound, one thread), forward + autograd backward, {dt:.1f} s, not extrapolated"}
 
 
 def run_reference(args, wl, rank):
     if rank != 0:
         return
-    per_step = []
-    rows = None
-    for i in range(args.warmup + args.steps):
-        v, threads, rows, dt = cpu_rows_per_s(wl, args.cpu_seconds / max(1, args.steps), rows=rows)
-        if i >= args.warmup:
-            per_step.append((rows, dt))
-    tot_rows = sum(r for r, _ in per_step)
-    tot_t = sum(t for _, t in per_step)
-    value = tot_rows / tot_t
-    sample = f"{rows} of {wl['B']} rows of the workload per step, vectorised torch-CPU restatement of torch_ref, forward + autograd backward"
+    base, med, times = cpu_port_rows_per_s(wl, steps=max(1, args.steps), warmup=max(1, args.warmup))
+    value = base["value"]
     line = {
         "impl": "reference", "metric": "ncn_fwd_bwd_rows_per_s", "value": value, "unit": "rows/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * tot_t / max(1, len(per_step)),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * med,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": wl["desc"], "rows": wl["B"], "D": wl["N"], "g": wl["n"], "stages": wl["L"],
-                   "activation": wl["act"]},
-        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": config_of(wl, args.mode, args.gpus),
+        "cpu_baseline": base,
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    lit = cpu_literal_rows_per_s()
+    if lit is not None:
+        line["cpu_reference_literal"] = lit
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------ GPU arm
-def run_b200(args, wl, rank, world, local_rank):
+def kernel_names(wl, mode):
+    """The kernels the library picks for this workload (for the roofline label)."""
+    if wl.get("E", 1) > 1:
+        return "feat_fwd_kernel (ncn_feat.cuh)", "feat_bwd_kernel (ncn_feat.cuh)"
+    n = wl["n"]
+    if n == 16 or mode == "recompute":
+        return "pair_fwd_dual_kernel (ncn_pairs.cuh)", "rows_bwd_kernel / pair_bwd_wide_kernel"
+    if n == 4 and wl["L"] <= 6:
+        return "lane_fwd_kernel (ncn_lanes.cuh)", "lanep_bwd_kernel (ncn_lanes_pipe.cuh)"
+    return "lane_fwd_kernel (ncn_lanes.cuh)", "lane_bwd_kernel (ncn_lanes.cuh)"
+
+
+def measure(ncn, name, wl, mode_override, dev, rank, world, steps, warmup, clocks_index=None):
+    """Device-resident timing of `steps` forward + backward steps of one workload.  Returns
+    (summary dict, objects needed by the e2e leg)."""
     import torch.distributed as dist
 
-    import ncn_cuda_b200 as ncn
-    from oracle import ncn_oracle as O  # used by the cpu_baseline leg only
-
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     dtype = torch.float32 if wl["dtype"] == "f32" else torch.bfloat16
     w = 4 if wl["dtype"] == "f32" else 2
     B, N, n, L = wl["B"], wl["N"], wl["n"], wl["L"]
     E, C = wl.get("E", 1), wl.get("C", 1)
-    mode = args.mode or wl.get("mode", "auto")
+    mode = mode_override or wl.get("mode", "auto")
     g = torch.Generator(device=dev).manual_seed(wl["seed"] + 1000 * rank)
     x = torch.randn(B, N, E, generator=g, device=dev, dtype=torch.float32).to(dtype).requires_grad_(True)
     xa = torch.zeros(B, N, E, device=dev, dtype=dtype).requires_grad_(True)
@@ -192,13 +246,13 @@ def run_b200(args, wl, rank, world, local_rank):
     layers = wl.get("layers", 0)
     if layers:
         net = ncn.NCNResidualStack(layers, 0.9, wl["act"], n, 1, L, 1, w_std=wl["w_var"] ** 0.5,
-                                   backward_mode="recompute" if mode == "auto" else mode).to(dev)
+                                   backward_mode="tape" if mode == "auto" else mode).to(dev)
         ws = [net.weight]
     else:
         ws = [(torch.randn(2 * E, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]
         net = ncn.NCNNetTestCuda(0.9, wl["act"], n, C, L, ws, backward_mode=mode)
 
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
 
     def step(i=None):
         x.grad = None; xa.grad = None
@@ -214,16 +268,16 @@ def run_b200(args, wl, rank, world, local_rank):
         if i is not None:
             ev[i][2].record()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(clocks_index if clocks_index is not None else dev.index) as clocks:
         t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
         t_start.record()
-        for i in range(args.steps):
+        for i in range(steps):
             step(i)
         t_end.record()
         torch.cuda.synchronize()
@@ -236,7 +290,7 @@ def run_b200(args, wl, rank, world, local_rank):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    ms_step = ms / args.steps
+    ms_step = ms / steps
     fwd_ms = sorted(e[0].elapsed_time(e[1]) for e in ev)[len(ev) // 2]
     bwd_ms = sorted(e[1].elapsed_time(e[2]) for e in ev)[len(ev) // 2]
     value = world * B / (ms_step * 1e-3)
@@ -249,45 +303,88 @@ def run_b200(args, wl, rank, world, local_rank):
     # every layer of a stack moves the same bytes; with several features per position every STAGE is
     # its own forward and backward kernel and moves them again
     per_stage = E > 1
-    elems = B * N * E * max(1, layers) * (L if per_stage else 1)
+    launches = max(1, layers) * (L if per_stage else 1)  # backward launches per step
+    elems = B * N * E * launches
     bwd_bytes = 6 * w * elems  # reads y, ya, dy, dya; writes dx, dxa
     bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9
     step_gbs = 10 * w * elems / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+    fk, bk = kernel_names(wl, mode)
     roofline = {
-        "bound": "hbm", "kernel": ("feat_bwd_kernel (ncn_feat.cuh), %d launches per step" % L if per_stage
-                                   else "pair_bwd_dual_kernel (ncn_pairs.cuh)" if n <= 8 and mode != "recompute" and not (dtype != torch.float32 and mode == "auto")
-                                   else "rows_bwd_kernel / pair_bwd_wide_kernel"), "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
-        "unit": "GB/s", "frac": bwd_gbs / peak, "ms_per_launch": bwd_ms / (L if per_stage else 1),
-        # measured on the cfg2 shape (fp32, one checkpoint); traffic grows in proportion to the rows
-        "traffic": (BWD_TRAFFIC_BYTES_PER_ELEMENT * elems if args.workload in ("cfg2", "small") and mode == "auto" else None),
-        "algorithmic_bytes": bwd_bytes // (L if per_stage else 1),
+        "bound": "hbm", "kernel": bk + (", %d launches per step" % launches if launches > 1 else ""),
+        "forward_kernel": fk, "achieved": bwd_gbs, "peak": peak, "peak_source": peak_src,
+        "unit": "GB/s", "frac": bwd_gbs / peak, "ms_per_launch": bwd_ms / launches,
+        # measured on the 8192-row case of the cfg2 shape (fp32, one stored state), scaled by the elements
+        "traffic": (BWD_TRAFFIC_BYTES_PER_ELEMENT * elems if name in ("cfg2", "small") and mode == "auto" else None),
+        "algorithmic_bytes": bwd_bytes // launches,
         "fwd_plus_bwd": {"achieved": step_gbs, "frac": step_gbs / peak, "frac_of_8TBs_nominal": step_gbs / 8000.0,
                          "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "algorithmic_bytes": 10 * w * elems},
-        "note": "issue-bound kernel (n*L dependent tanh steps per element); HBM fraction reported as the metric asks",
+        "note": "bound by the FMA and special-function pipes (n*L dependent tanh steps per element), not by HBM; "
+                "the HBM fraction is reported because the metric asks for it",
     }
+    summary = {
+        "value": value, "unit": "rows/s", "ms_per_step": ms_step, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "mode": mode,
+        "dtype": wl["dtype"], "rows_per_s_per_gpu": value / world, "roofline": roofline,
+        "gpu_launches": (3 * L if per_stage else 3) * steps * max(1, layers), "clocks": clocks.summary(),
+        "steps": steps, "warmup": warmup, "config": config_of(wl, mode, world),
+    }
+    return summary, (dtype, ws, mode, layers, per_stage)
 
+
+def run_b200(args, wl, rank, world, local_rank):
+    import torch.distributed as dist
+
+    import ncn_cuda_b200 as ncn
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    m, (dtype, ws, mode, layers, per_stage) = measure(ncn, args.workload, wl, args.mode, dev, rank, world, args.steps,
+                                                      args.warmup, local_rank)
     line = {
-        "metric": "ncn_fwd_bwd_rows_per_s", "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "metric": "ncn_fwd_bwd_rows_per_s", "value": m["value"], "unit": "rows/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": wl["desc"], "rows_per_gpu": B, "D": N, "E": E, "heads": C, "g": n, "stages": L, "activation": wl["act"],
-                   "backward_mode": mode, "parallelism": f"dp{world}", "l2": "inputs larger than L2 (%.2f GB per tensor)" % (B * N * E * w / 1e9)},
-        "roofline": roofline, "gpu_launches": (3 * L if per_stage else 3) * args.steps * max(1, layers), "clocks": clocks.summary(),
-        "rows_per_s_per_gpu": value / world,
+        "config": m["config"], "roofline": m["roofline"], "gpu_launches": m["gpu_launches"], "clocks": m["clocks"],
+        "rows_per_s_per_gpu": m["rows_per_s_per_gpu"],
     }
 
     if not args.no_e2e and not layers and not per_stage:
         e2e = run_e2e(ncn, wl, dev, dtype, ws, mode, world, rank)  # every rank: its rows through its own host buffers
         if rank == 0:
             line["e2e"] = e2e
+    del ws
+    torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
+
+    # the other configurations, a few steps each (device-resident figures; same timing rules)
+    if not args.no_extra and args.workload == "cfg2":
+        extra = {}
+        for name in (EXTRA_1GPU if world == 1 else EXTRA_NGPU):
+            try:
+                em, keep = measure(ncn, name, WORKLOADS[name], None, dev, rank, world, args.extra_steps, 3, local_rank)
+                del keep
+                extra[name] = {k: em[k] for k in ("value", "unit", "ms_per_step", "fwd_ms", "bwd_ms", "mode", "dtype",
+                                                  "rows_per_s_per_gpu", "steps", "warmup")}
+                extra[name]["workload"] = WORKLOADS[name]["desc"]
+                extra[name]["roofline_frac_bwd"] = em["roofline"]["frac"]
+                extra[name]["roofline_frac_fwd_plus_bwd"] = em["roofline"]["fwd_plus_bwd"]["frac"]
+                extra[name]["kernels"] = [em["roofline"]["forward_kernel"], em["roofline"]["kernel"]]
+                extra[name]["clocks"] = em["clocks"]
+            except RuntimeError as e:  # e.g. a device too small for the largest configuration
+                extra[name] = {"error": str(e).splitlines()[0][:200]}
+            torch.cuda.empty_cache()
+            if world > 1:
+                dist.barrier()
+        line["workloads"] = extra
+
     if rank == 0 and world == 1 and not args.no_cpu and not layers:
-        v, threads, rows, dt = cpu_rows_per_s(wl, args.cpu_seconds)
-        line["cpu_baseline"] = {
-            "value": v, "unit": "rows/s", "cores": threads, "kind": "port",
-            "sample": f"{rows} of {B} rows, vectorised torch-CPU restatement of torch_ref, forward + autograd backward, {dt:.1f} s",
-        }
+        base, _, _ = cpu_port_rows_per_s(wl)
+        line["cpu_baseline"] = base
+        lit = cpu_literal_rows_per_s()
+        if lit is not None:
+            line["cpu_reference_literal"] = lit
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

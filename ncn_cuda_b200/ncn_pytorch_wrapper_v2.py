@@ -74,17 +74,21 @@ def plan_backward(dtype, n_cache: int, num_modules: int, residual: bool, backwar
                   applied across all stages; nothing but the output is stored)
     "checkpoint"  as invert, but the forward also stores the state every few stages so that no
                   inverse chain exceeds MAX_INVERSE_STEPS steps
-    "recompute"   store the net input and replay the forward in fp32 inside the backward kernel
+    "recompute"   store the net input and replay the forward in fp32 inside the backward kernel; the
+                  replay keeps no intermediate state, so the walk back inverts all n_cache * L steps
+                  and fp32 gradients lose accuracy beyond MAX_INVERSE_STEPS steps (about 5e-5 at 32
+                  steps, 3e-3 at 64): the memory-lean choice for bf16 storage
     "tape"        as checkpoint, and the fp32 state after the last stage is stored too: the backward
                   starts from it and reads neither the net input nor its output.  The faster choice
                   for bf16 storage and residual layers (no replay) at 8 more bytes per element;
                   with bf16 storage the periodic states are four times sparser
-    "auto"        recompute for bf16 storage and residual layers, else checkpoint
+    "auto"        tape for bf16 storage and residual layers (exact starting state, no inverse chain
+                  beyond MAX_INVERSE_STEPS in fp32), else checkpoint
     """
     if backward_mode not in ("auto", "invert", "checkpoint", "recompute", "tape"):
         raise ValueError(f"unknown backward_mode {backward_mode!r}")
     if backward_mode == "auto":
-        backward_mode = "recompute" if (dtype != torch.float32 or residual) else "checkpoint"
+        backward_mode = "tape" if (dtype != torch.float32 or residual) else "checkpoint"
     if residual and backward_mode not in ("recompute", "tape"):
         raise ValueError("residual layers need backward_mode='recompute' or 'tape'")
     if backward_mode == "recompute":
@@ -106,13 +110,15 @@ class NCNNetFunction(torch.autograd.Function):
     def forward(ctx, x, xa, W, alpha, activation, n_cache, n_head, first_module, backward_mode, residual):
         recompute, every, tape = plan_backward(x.dtype, n_cache, W.shape[0], residual, backward_mode)
         y, ya, ckpt = ops.net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module, every, residual, tape)
+        # The stored states go through save_for_backward like the other saved tensors: autograd
+        # frees them after the backward and raises its usual error on a second backward without
+        # retain_graph, instead of a backward that silently finds no stored state.
         if tape:
-            ctx.save_for_backward(W)  # the stored states are all the backward reads
+            ctx.save_for_backward(W, ckpt)  # the stored states are all the backward reads
         elif recompute:
-            ctx.save_for_backward(x, xa, W)
+            ctx.save_for_backward(x, xa, W, ckpt)
         else:
-            ctx.save_for_backward(y, ya, W)
-        ctx.ckpt = ckpt
+            ctx.save_for_backward(y, ya, W, ckpt)
         ctx.cfg = (alpha, activation, n_cache, n_head, first_module, every, recompute, residual, tape)
         return y, ya
 
@@ -120,15 +126,16 @@ class NCNNetFunction(torch.autograd.Function):
     def backward(ctx, dy, dya):
         alpha, activation, n_cache, n_head, first_module, every, recompute, residual, tape = ctx.cfg
         if tape:
-            (W,) = ctx.saved_tensors
+            W, ckpt = ctx.saved_tensors
             s0 = s1 = None
         else:
-            s0, s1, W = ctx.saved_tensors
+            s0, s1, W, ckpt = ctx.saved_tensors
+        if ckpt is None and (tape or (every > 0 and not recompute and W.shape[0] > every)):
+            raise RuntimeError("the stored states of this net forward are gone; cannot run its backward")
         dx, dxa, dW = ops.net_bwd(
             s0, s1, dy, dya, W, alpha, activation, n_cache, n_head, first_module,
-            ckpt=ctx.ckpt, ckpt_every=every, recompute=recompute, residual=residual, tape=tape,
+            ckpt=ckpt, ckpt_every=every, recompute=recompute, residual=residual, tape=tape,
         )
-        ctx.ckpt = None
         return dx, dxa, dW.to(W.dtype), None, None, None, None, None, None, None
 
 

@@ -19,11 +19,13 @@ from .ncn_pytorch_wrapper_v2 import fused_ncn_net
 class NCNResidualStack(nn.Module):
     """`num_layers` layers; layer k is an NCN net of `num_modules` stages with
     x <- x + net(x, xa).x and xa <- net(x, xa).xa.  weight: [num_layers, num_modules, 2*embed_dim].
-    backward_mode: "recompute" keeps each layer's input and replays its forward in the backward;
-    "tape" keeps the layer's fp32 end state (and periodic ones) instead: no replay, more memory."""
+    backward_mode: "tape" (default) keeps each layer's fp32 end state (and periodic ones): no replay,
+    fp32 gradients at full accuracy; "recompute" keeps each layer's input instead and replays its
+    forward in the backward: less memory, and in fp32 a loss of accuracy once n_cache * num_modules
+    exceeds 16 steps (see plan_backward)."""
 
     def __init__(self, num_layers, alpha, activation, n_cache, n_head, num_modules, embed_dim, w_std=None,
-                 backward_mode="recompute"):
+                 backward_mode="tape"):
         super().__init__()
         self.num_layers = num_layers
         self.alpha = alpha

@@ -104,11 +104,15 @@ def test_bf16_beyond_2_31_elements(ncn):
     sy, sya, sdx, sdxa, sdW = _run(ncn, x[lo:hi].clone(), xa[lo:hi].clone(), dy[lo:hi].clone(), dya[lo:hi].clone(), W, n, 0, recompute=True)
     assert torch.equal(sy, y[lo:hi]) and torch.equal(sdx, dx[lo:hi]) and torch.equal(sdxa, dxa[lo:hi])
     ws = [W[l].cpu() for l in range(L)]
-    ry, rya, rdx, rdxa, _ = O.net_fwd_bwd(x[lo:hi].float().cpu(), xa[lo:hi].float().cpu(), ws, dy[lo:hi].float().cpu(),
-                                          dya[lo:hi].float().cpu(), 0.9, "tanh", n, 1)
+    ry, rya, rdx, rdxa, rdW = O.net_fwd_bwd(x[lo:hi].float().cpu(), xa[lo:hi].float().cpu(), ws, dy[lo:hi].float().cpu(),
+                                            dya[lo:hi].float().cpu(), 0.9, "tanh", n, 1)
     assert O.rel_err(sy.float(), ry) < 2e-2 and O.rel_err(sya.float(), rya) < 2e-2
     assert O.rel_err(sdx.float(), rdx) < 2e-2 and O.rel_err(sdxa.float(), rdxa) < 2e-2
+    # the weight gradient: the slice against the oracle, and the whole batch as the sum over its parts
+    assert O.rel_err(sdW, torch.stack(list(rdW))) < 2e-2, O.rel_err(sdW, torch.stack(list(rdW)))
+    head = _run(ncn, x[:lo], xa[:lo], dy[:lo], dya[:lo], W, n, 0, recompute=True)[4]
     assert torch.isfinite(dW).all()
+    assert O.rel_err(head + sdW, dW) < 1e-4, O.rel_err(head + sdW, dW)
 
 
 def test_residual_stack_bf16_slice(ncn):
@@ -131,7 +135,27 @@ def test_residual_stack_bf16_slice(ncn):
     # bf16 rounding of 12 stored layer boundaries accumulates: 2e-2 per tensor is the stated bound
     assert O.rel_err(y[:rows].float(), ry) < 2e-2 and O.rel_err(ya[:rows].float(), rya) < 2e-2
     assert O.rel_err(x.grad[:rows].float(), rdx) < 2e-2 and O.rel_err(xa.grad[:rows].float(), rdxa) < 2e-2
-    assert torch.isfinite(stack.weight.grad).all()
+    # the weight gradient (what the data-parallel sum carries): the first rows alone against the oracle on
+    # those rows, and the whole batch as the sum over four quarters
+    full = stack.weight.grad.clone()
+    assert torch.isfinite(full).all()
+
+    def grad_of(lo, hi):
+        stack.weight.grad = None
+        xs = x[lo:hi].detach().clone().requires_grad_()
+        xas = xa[lo:hi].detach().clone().requires_grad_()
+        ys, yas = stack(xs, xas)
+        torch.autograd.backward([ys, yas], [dy[lo:hi], torch.zeros_like(dy[lo:hi])])
+        return stack.weight.grad.clone()
+
+    rows_w = 64
+    _, _, _, _, rdW = O.stack_fwd_bwd(x[:rows_w].detach().float().cpu(), xa[:rows_w].detach().float().cpu(), lws,
+                                      dy[:rows_w].float().cpu(), torch.zeros(rows_w, N, 1), 0.9, "tanh", n, 1)
+    want = torch.stack([torch.stack(list(r)) for r in rdW])
+    got = grad_of(0, rows_w).cpu()
+    assert O.rel_err(got, want) < 2e-2, O.rel_err(got, want)
+    acc = sum(grad_of(k * (B // 4), (k + 1) * (B // 4)) for k in range(4))
+    assert O.rel_err(acc, full) < 1e-4, O.rel_err(acc, full)
 
 
 def test_multi_feature_stage_full_size(ncn):
