@@ -1,11 +1,10 @@
-"""The ctypes stand-in for the reference's compiled extension, exactly as INTEGRATION.md prints it
-(`ncn_cuda_module.forward / backward`, ncn_cuda/ncn_cuda.cpp:29-32), executed from the document:
+"""The ctypes stand-in for the reference's compiled extension (tests/c_abi/ncn_cuda_module_stub.py:
+`ncn_cuda_module.forward / backward`, ncn_cuda/ncn_cuda.cpp:29-32):
 it must load the library, return what the reference's wrapper expects
 (ncn_cuda/ncn_pytorch_wrapper_v2.py:12-21, 35-48) and agree with the oracle — and, where the
 reference's own extension is built (oracle/_ref), with that one call for call."""
+import importlib.util
 import os
-import re
-import types
 
 import pytest
 import torch
@@ -20,12 +19,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.fixture(scope="module")
 def stub():
-    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
-    m = re.search(r"```python\n(# ncn_cuda_module\.py.*?)```", text, re.S)
-    assert m, "INTEGRATION.md no longer carries the ncn_cuda_module.py stub"
-    code = m.group(1).replace("/path/to/libncn_b200.so", os.path.join(ROOT, "ncn_cuda_b200", "libncn_b200.so"))
-    mod = types.ModuleType("ncn_cuda_module_stub")
-    exec(compile(code, "INTEGRATION.md:ncn_cuda_module.py", "exec"), mod.__dict__)
+    path = os.path.join(ROOT, "tests", "c_abi", "ncn_cuda_module_stub.py")
+    spec = importlib.util.spec_from_file_location("ncn_cuda_module_stub", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
     return mod
 
 
