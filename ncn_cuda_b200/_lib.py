@@ -46,6 +46,7 @@ SIGNATURES = {
     "ncn_status_string": (c_char_p, [c_int]),
     "ncn_last_cuda_error": (c_char_p, []),
     "ncn_version": (c_int, []),
+    "ncn_reload_env": (None, []),
 }
 
 _lib = None

@@ -55,12 +55,42 @@ static int get_dev(DevInfo& out) {
   return NCN_OK;
 }
 
+// Tuning switches of the environment, read once per process (they select among kernels for A/B
+// measurements; the defaults are the fastest measured).
+struct EnvSwitches {
+  bool exact_tanh, no_pair, no_feat, bwd_wide_off, bwd_dual_off, fwd_dual_off, lanes_off, lanes_pipe_off;
+  int fwd_threads, bwd_threads, nbuf;
+};
+static EnvSwitches read_env_switches() {
+  auto is = [](const char* name, char c) {
+    const char* e = std::getenv(name);
+    return e && e[0] == c;
+  };
+  auto num = [](const char* name) {
+    const char* e = std::getenv(name);
+    return e ? std::atoi(e) : 0;
+  };
+  EnvSwitches v;
+  v.exact_tanh = is("NCN_EXACT_TANH", '1');
+  v.no_pair = is("NCN_NO_PAIR", '1');
+  v.no_feat = is("NCN_NO_FEAT", '1');
+  v.bwd_wide_off = is("NCN_BWD_WIDE", '0');
+  v.bwd_dual_off = is("NCN_BWD_DUAL", '0');
+  v.fwd_dual_off = is("NCN_FWD_DUAL", '0');
+  v.lanes_off = is("NCN_LANES", '0');
+  v.lanes_pipe_off = is("NCN_LANES_PIPE", '0');
+  v.fwd_threads = num("NCN_FWD_THREADS");
+  v.bwd_threads = num("NCN_BWD_THREADS");
+  v.nbuf = num("NCN_NBUF");
+  return v;
+}
+static EnvSwitches g_env = read_env_switches();
+static std::atomic<int> g_plan_epoch{0};  // bumped by ncn_reload_env: cached launch plans of older epochs are stale
+static const EnvSwitches& env_switches() { return g_env; }
+
 // tanh with bf16 storage runs on tanh.approx inside the fused kernels (NCN_EXACT_TANH=1 turns that off)
 static int fused_act(int act, int dtype) {
-  if (act == ACT_TANH && dtype == DT_BF16) {
-    const char* e = std::getenv("NCN_EXACT_TANH");
-    if (!(e && e[0] == '1')) return ACT_TANH_FAST;
-  }
+  if (act == ACT_TANH && dtype == DT_BF16 && !env_switches().exact_tanh) return ACT_TANH_FAST;
   return act;
 }
 
@@ -133,8 +163,7 @@ static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, i
   const int w = dtype == DT_BF16 ? 2 : 4;
   const int m = N / n;
   // fast path: one pair of groups (g, g + m/2) per thread, if a row's pairs fit one CTA
-  const char* nopair = std::getenv("NCN_NO_PAIR");
-  pl.pair = pair_fn(n, bwd) != nullptr && m % 2 == 0 && m / 2 <= pair_max_threads(n, bwd) && !(nopair && nopair[0] == '1');
+  pl.pair = pair_fn(n, bwd) != nullptr && m % 2 == 0 && m / 2 <= pair_max_threads(n, bwd) && !env_switches().no_pair;
   const bool wide = bwd && pl.pair && want_wide && !want_dual;
   const bool dual = bwd && pl.pair && want_dual && n <= 8 && !(flags & F_RECOMPUTE);
   if (want_dual && (bwd ? !dual : !pl.pair)) return NCN_ERR_UNSUPPORTED;
@@ -224,11 +253,11 @@ static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, i
   const int items = pl.pair ? m / 2 : m;  // work items per row
   int maxT = pl.pair ? pair_max_threads(n, bwd) : rows_max_threads(n, bwd);
   int force_nbuf = 0;
-  if (const char* e = std::getenv(bwd ? "NCN_BWD_THREADS" : "NCN_FWD_THREADS")) {  // tuning experiments
-    const int t = std::atoi(e);
+  {  // tuning experiments
+    const int t = bwd ? env_switches().bwd_threads : env_switches().fwd_threads;
     if (t >= 32 && t <= maxT && t % 32 == 0) maxT = t;
   }
-  if (const char* e = std::getenv("NCN_NBUF")) force_nbuf = std::atoi(e);
+  force_nbuf = env_switches().nbuf;
   const bool recompute = (flags & F_RECOMPUTE) != 0;
   if (recompute) n_ck = 0;
   int R = items >= maxT ? 1 : maxT / items;
@@ -298,15 +327,13 @@ static int plan_rows_impl(bool bwd, int64_t B, int N, int n, int L, int dtype, i
 // Pair backward: the variant with separate buffers (one CTA per SM, full register budget, next
 // tile prefetched) measured slightly faster than the aliased one (two CTAs per SM) and is tried
 // first; NCN_BWD_WIDE=0 forces the aliased variant.
-static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
-                     const DevInfo& dev, int act, Plan& pl) {
-  const char* wide_env = std::getenv("NCN_BWD_WIDE");
-  const bool allow_wide = !(wide_env && wide_env[0] == '0');
+static int plan_rows_uncached(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
+                              const DevInfo& dev, int act, Plan& pl) {
+  const bool allow_wide = !env_switches().bwd_wide_off;
   // Plain backward of small groups: two pairs per thread in the aliased tile buffer, two CTAs per
   // SM with a full register budget; measured 6-8 % faster than the wide variant.  NCN_BWD_DUAL=0
   // switches it off.
-  const char* dual_env = std::getenv("NCN_BWD_DUAL");
-  if (bwd && !(dual_env && dual_env[0] == '0')) {
+  if (bwd && !env_switches().bwd_dual_off) {
     Plan trial;
     const int rc = plan_rows_impl(true, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, false, trial, true);
     if (rc == NCN_OK && trial.pair && trial.variant == 2) {
@@ -324,8 +351,7 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   }
   // Forward of small groups: one tile buffer, two pairs per thread, four CTAs per SM.
   // NCN_FWD_DUAL=0 switches it off.
-  const char* fdual_env = std::getenv("NCN_FWD_DUAL");
-  if (!bwd && !(fdual_env && fdual_env[0] == '0')) {
+  if (!bwd && !env_switches().fwd_dual_off) {
     Plan trial;
     const int rc = plan_rows_impl(false, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, false, trial, true);
     if (rc == NCN_OK && trial.pair && trial.variant >= 2) {
@@ -335,6 +361,39 @@ static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int fl
   }
   pl = Plan();
   return plan_rows_impl(bwd, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, false, pl);
+}
+
+// A plan costs up to three layouts, each with a cudaFuncSetAttribute and an occupancy query; it
+// depends on nothing but these arguments and the device, so it is computed once per argument set.
+struct RowsKey {
+  int epoch, dev, bwd, N, n, L, dtype, flags, n_ck, want_rec, act;
+  long long B;
+  bool operator==(const RowsKey& o) const {
+    return epoch == o.epoch && dev == o.dev && bwd == o.bwd && N == o.N && n == o.n && L == o.L && dtype == o.dtype && flags == o.flags &&
+           n_ck == o.n_ck && want_rec == o.want_rec && act == o.act && B == o.B;
+  }
+};
+
+static int plan_rows(bool bwd, int64_t B, int N, int n, int L, int dtype, int flags, int n_ck, bool want_rec,
+                     const DevInfo& dev, int act, Plan& pl) {
+  static std::mutex mu;
+  static std::vector<std::pair<RowsKey, std::pair<int, Plan>>> cache;
+  const RowsKey key{g_plan_epoch.load(), dev.dev, bwd ? 1 : 0, N, n, L, dtype, flags, n_ck, want_rec ? 1 : 0, act, (long long)B};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (auto& kv : cache)
+      if (kv.first == key) {
+        pl = kv.second.second;
+        return kv.second.first;
+      }
+  }
+  const int rc = plan_rows_uncached(bwd, B, N, n, L, dtype, flags, n_ck, want_rec, dev, act, pl);
+  if (rc != NCN_ERR_CUDA) {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() >= 64) cache.erase(cache.begin());
+    cache.emplace_back(key, std::make_pair(rc, pl));
+  }
+  return rc;
 }
 
 // ---- register-resident row kernels (ncn_lanes.cuh)
@@ -350,20 +409,10 @@ static LaneLaunchFn lane_fn(int n, bool bwd) {
 }
 
 // NCN_LANES=0 switches the family off (A/B measurements); read once.
-static bool lanep_enabled() {  // NCN_LANES_PIPE=0: the plain register-resident backward instead of the pipelined one
-  static const bool on = [] {
-    const char* e = std::getenv("NCN_LANES_PIPE");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-static bool lanes_enabled() {
-  static const bool on = [] {
-    const char* e = std::getenv("NCN_LANES");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
+// NCN_LANES=0 switches the register-resident family off, NCN_LANES_PIPE=0 its pipelined backward
+// (A/B measurements).
+static bool lanep_enabled() { return !env_switches().lanes_pipe_off; }
+static bool lanes_enabled() { return !env_switches().lanes_off; }
 
 struct LanePlan {
   int threads = 0, R = 0, grid = 0, tpr = 0, ea_max = 0, occ = 0;
@@ -463,10 +512,10 @@ static bool lanep_layout(int N, int L, int dtype, int flags, int n_ck, int R, in
 }
 
 struct LaneKey {
-  int dev, bwd, N, n, L, l0, dtype, flags, n_ck, act;
+  int epoch, dev, bwd, N, n, L, l0, dtype, flags, n_ck, act;
   long long B;
   bool operator==(const LaneKey& o) const {
-    return dev == o.dev && bwd == o.bwd && N == o.N && n == o.n && L == o.L && l0 == o.l0 && dtype == o.dtype &&
+    return epoch == o.epoch && dev == o.dev && bwd == o.bwd && N == o.N && n == o.n && L == o.L && l0 == o.l0 && dtype == o.dtype &&
            flags == o.flags && n_ck == o.n_ck && act == o.act && B == o.B;
   }
 };
@@ -481,7 +530,7 @@ static int plan_lanes(bool bwd, int64_t B, int64_t N, int64_t E, int n, int C, i
   if (!lane_shape_ok(N, E, n, C, l0, L, dtype, &e_need)) return NCN_ERR_UNSUPPORTED;
   static std::mutex mu;
   static std::vector<std::pair<LaneKey, std::pair<int, LanePlan>>> cache;
-  const LaneKey key{dev.dev, bwd ? 1 : 0, (int)N, n, L, l0, dtype, flags & (F_RESIDUAL | F_TAPE), n_ck, act, (long long)B};
+  const LaneKey key{g_plan_epoch.load(), dev.dev, bwd ? 1 : 0, (int)N, n, L, l0, dtype, flags & (F_RESIDUAL | F_TAPE), n_ck, act, (long long)B};
   {
     std::lock_guard<std::mutex> lk(mu);
     for (auto& kv : cache)
@@ -662,9 +711,7 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
   const int gpw = feat_groups_per_warp(n, d);
   FeatLaunchFn fn = feat_fn(n, bwd);
   if (gpw == 0 || fn == nullptr) return NCN_ERR_UNSUPPORTED;
-  if (const char* e = std::getenv("NCN_NO_FEAT")) {  // tuning experiments: force the shared-memory kernels
-    if (e[0] == '1') return NCN_ERR_UNSUPPORTED;
-  }
+  if (env_switches().no_feat) return NCN_ERR_UNSUPPORTED;  // tuning experiments: force the shared-memory kernels
   const int act = fused_act(map_act(activation), dtype);
   for (int q = 0; q < (bwd ? 4 : 2); ++q)
     if (!aligned16(in[q])) return NCN_ERR_UNSUPPORTED;
@@ -714,7 +761,12 @@ using namespace ncn;
 
 extern "C" {
 
-int ncn_version(void) { return 100; }
+int ncn_version(void) { return 101; }
+
+void ncn_reload_env(void) {
+  g_env = read_env_switches();
+  g_plan_epoch.fetch_add(1);
+}
 
 const char* ncn_status_string(int s) {
   switch (s) {

@@ -64,8 +64,9 @@ def test_plan_backward():
     assert plan_backward(f32, 4, 3, False, "auto") == (False, 0, False)      # 12 steps: nothing to store
     assert plan_backward(f32, 16, 4, False, "checkpoint") == (False, 1, False)
     assert plan_backward(f32, 4, 6, False, "invert") == (False, 0, False)
-    assert plan_backward(bf16, 16, 4, False, "auto") == (True, 0, False)
-    assert plan_backward(f32, 8, 4, True, "auto") == (True, 0, False)
+    assert plan_backward(bf16, 16, 4, False, "auto") == (False, 0, True)    # bf16 storage: the stored end state
+    assert plan_backward(f32, 8, 4, True, "auto") == (False, 2, True)       # residual layer: stored states, no replay
+    assert plan_backward(bf16, 16, 4, False, "recompute") == (True, 0, False)
     assert plan_backward(bf16, 16, 4, False, "tape") == (False, 0, True)   # 64 steps from the fp32 end state
     assert plan_backward(bf16, 16, 8, False, "tape") == (False, 4, True)
     assert plan_backward(f32, 8, 4, True, "tape") == (False, 2, True)
@@ -154,14 +155,17 @@ def test_gradient_sum_over_two_gloo_ranks(tmp_path):
 def test_bench_reference_arm_prints_contract_line():
     import json
 
-    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
-                          "--cpu-seconds", "1"], capture_output=True, text=True, timeout=600)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stderr[-2000:]
     line = json.loads(res.stdout.strip().splitlines()[-1])
     for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
                 "dtype", "data", "config", "cpu_baseline", "e2e"):
         assert key in line, key
     assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port" and line["value"] > 0
+    assert "rows_per_gpu" in line["config"] and "backward_mode" in line["config"]  # the GPU arm's config keys
+    if "cpu_reference_literal" in line:  # present where oracle/_ref/ holds the reference's torch_ref files
+        assert line["cpu_reference_literal"]["kind"] == "reference" and line["cpu_reference_literal"]["value"] > 0
 
 
 def test_host_pipeline_chunk_bounds():

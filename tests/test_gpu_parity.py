@@ -222,9 +222,16 @@ def test_feat_matches_shared_memory_kernels(ncn, monkeypatch):
     a = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
     a2 = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
     assert all(torch.equal(u, v) for u, v in zip(a, a2))  # reproducible, dW included
+    from ncn_cuda_b200 import _lib
+
     monkeypatch.setenv("NCN_NO_FEAT", "1")
-    y2, ya2 = ncn.ops.stage_fwd(x, xa, W, 0.9, 0, n, C, l)
-    b = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
+    _lib.load().ncn_reload_env()  # the switches are read once per process unless asked again
+    try:
+        y2, ya2 = ncn.ops.stage_fwd(x, xa, W, 0.9, 0, n, C, l)
+        b = ncn.ops.stage_bwd(y, ya, dy, dya, W, 0.9, 0, n, C, l)
+    finally:
+        monkeypatch.delenv("NCN_NO_FEAT")
+        _lib.load().ncn_reload_env()
     assert O.rel_err(y, y2) < 2e-6 and O.rel_err(ya, ya2) < 2e-6
     for u, v in zip(a, b):
         assert O.rel_err(u, v) < TOL32
