@@ -102,12 +102,14 @@ __device__ __forceinline__ void act_r_all(const float2 (&ts)[NG], float2 (&r)[NG
   }
 }
 
-#ifndef NCN_FWD_BATCH
-#define NCN_FWD_BATCH 4
-#endif
-#ifndef NCN_BWD_BATCH
-#define NCN_BWD_BATCH 4
-#endif
+// Measured on the arithmetic alone (microbench.cu): the forward is bound by the special-function pipe
+// and wants the largest batch; the backward is bound by the FMA pipe, where groups of 8 do better
+// with batches of two (17.3 against 18.5 cycles per warp.position.step), groups of 4 with four.
+template <int NG>
+struct LaneBatch {
+  static constexpr int fwd = 4;
+  static constexpr int bwd = NG >= 8 ? 2 : 4;
+};
 
 // ------------------------------------------------------------------ step math (scaled variables of ncn_common.cuh)
 template <int NG, int ACT, int J>
@@ -132,7 +134,7 @@ struct LFwdSteps {
     float2 ts[NG], r[NG];
 #pragma unroll
     for (int i = 0; i < NG; ++i) ts[i] = ffma2(X[i], P, Q);
-    act_r_all<ACT, NG, NCN_FWD_BATCH>(ts, r);
+    act_r_all<ACT, NG, LaneBatch<NG>::fwd>(ts, r);
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
       A[i] = ffma2(r[i], f2(cA), A[i]);
@@ -192,7 +194,7 @@ struct LBwdSteps {
     float2 ts[NG], r[NG];
 #pragma unroll
     for (int i = 0; i < NG; ++i) ts[i] = ffma2(X[i], Ps, Qs);
-    act_r_all<ACT, NG, NCN_BWD_BATCH>(ts, r);
+    act_r_all<ACT, NG, LaneBatch<NG>::bwd>(ts, r);
     float2 aI = f2(0.0f), aS = f2(0.0f);
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
