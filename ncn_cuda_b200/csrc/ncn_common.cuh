@@ -322,6 +322,52 @@ struct ActForm<ACT_LINEAR> {
   static __device__ __forceinline__ float2 gt(float2 g, float2, float2) { return g; }
 };
 
+// r = 1 / (1 + 2^ts) for all N values of an array at once (the positions of a group, or the features of a
+// position).
+// BATCH: reciprocals taken from one special-function reciprocal of the product of BATCH values
+// (4: 1.25, 2: 1.5, 1: 2 special-function instructions per position and step; the smaller the batch
+// the fewer multiplies on the FMA pipe).
+template <int ACT, int NG, int BATCH>
+__device__ __forceinline__ void act_r_all(const float2 (&ts)[NG], float2 (&r)[NG]) {
+  if constexpr (ACT == ACT_TANH || ACT == ACT_SIGMOID) {
+    // r_i = 1 / d_i, d_i = 1 + 2^ts_i.  The exponent is capped at 30: beyond it r < 1e-9 (tanh = 1 to the last
+    // bit) and the product of four d stays a normal fp32 number, as does its reciprocal.
+    float2 d[NG];
+#pragma unroll
+    for (int i = 0; i < NG; ++i)
+      d[i] = __fadd2_rn(make_float2(ex2_approx(fminf(ts[i].x, 30.0f)), ex2_approx(fminf(ts[i].y, 30.0f))), f2(1.0f));
+    if constexpr (BATCH == 1) {
+#pragma unroll
+      for (int i = 0; i < NG; ++i) r[i] = make_float2(rcp_approx(d[i].x), rcp_approx(d[i].y));
+    } else if constexpr (NG == 2 || BATCH == 2) {
+#pragma unroll
+      for (int b = 0; b < NG; b += 2) {
+        const float2 P = __fmul2_rn(d[b], d[b + 1]);
+        const float2 R = make_float2(rcp_approx(P.x), rcp_approx(P.y));
+        r[b] = __fmul2_rn(d[b + 1], R);
+        r[b + 1] = __fmul2_rn(d[b], R);
+      }
+    } else {
+#pragma unroll
+      for (int b = 0; b < NG; b += 4) {
+        const float2 P01 = __fmul2_rn(d[b], d[b + 1]);
+        const float2 P23 = __fmul2_rn(d[b + 2], d[b + 3]);
+        const float2 PP = __fmul2_rn(P01, P23);
+        const float2 R = make_float2(rcp_approx(PP.x), rcp_approx(PP.y));
+        const float2 i01 = __fmul2_rn(P23, R);
+        const float2 i23 = __fmul2_rn(P01, R);
+        r[b] = __fmul2_rn(d[b + 1], i01);
+        r[b + 1] = __fmul2_rn(d[b], i01);
+        r[b + 2] = __fmul2_rn(d[b + 3], i23);
+        r[b + 3] = __fmul2_rn(d[b + 2], i23);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NG; ++i) r[i] = ActForm<ACT>::r(ts[i]);
+  }
+}
+
 // forward offsets after k steps: C_k = sum_{i=1..k} c f0 / m^i ; D_k = sum_{i=1..k} c C_i
 constexpr double fwd_C(int k, double f0) {
   double C = 0.0;

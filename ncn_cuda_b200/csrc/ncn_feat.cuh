@@ -18,8 +18,13 @@
 #pragma once
 #include "ncn_common.cuh"
 
-#ifndef NCN_FEAT_FWD_NEWTON_EVERY
-#define NCN_FEAT_FWD_NEWTON_EVERY 2
+// Reciprocals of the tanh / sigmoid taken together over the feature pairs of a position (act_r_all,
+// ncn_common.cuh): 0 = one special-function reciprocal per value.
+#ifndef NCN_FEAT_FWD_BATCH
+#define NCN_FEAT_FWD_BATCH 4
+#endif
+#ifndef NCN_FEAT_BWD_BATCH
+#define NCN_FEAT_BWD_BATCH 0
 #endif
 #ifndef NCN_FEAT_UNROLL
 #define NCN_FEAT_UNROLL 1
@@ -171,17 +176,20 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatPar
 #pragma unroll
           for (int q = 0; q < KP; ++q) acc = __ffma2_rn(X[r][q], Wi[q], acc);
           const float2 sim = f2(red_sub<LD>(acc.x + acc.y + cj));  // sT (1-alpha)(x_i.Wi + x_j.Wj)
+          // the forward is bound by the special-function unit: the reciprocals of a position's feature
+          // pairs come from one reciprocal of their product
+          float2 ts[KP], rr[KP];
+#pragma unroll
+          for (int q = 0; q < KP; ++q) ts[q] = __ffma2_rn(sim, xj[q], __fmul2_rn(X[r][q], alpha_s));
+          if constexpr (KP >= 2 && NCN_FEAT_FWD_BATCH > 1) {
+            act_r_all<ACT, KP, NCN_FEAT_FWD_BATCH>(ts, rr);
+          } else {
+#pragma unroll
+            for (int q = 0; q < KP; ++q) rr[q] = F::r(ts[q]);
+          }
 #pragma unroll
           for (int q = 0; q < KP; ++q) {
-            const float2 ts = __ffma2_rn(sim, xj[q], __fmul2_rn(X[r][q], alpha_s));
-            float2 rr;
-            if constexpr (ACT == ACT_TANH && NCN_FEAT_FWD_NEWTON_EVERY > 0) {
-              // the forward is bound by the special-function unit: some of the reciprocals go to the FMA pipe
-              if ((q % NCN_FEAT_FWD_NEWTON_EVERY) == NCN_FEAT_FWD_NEWTON_EVERY - 1) rr = F::r_fma(ts); else rr = F::r(ts);
-            } else {
-              rr = F::r(ts);
-            }
-            A[r][q] = __ffma2_rn(rr, f2(cf1), __ffma2_rn(A[r][q], f2(kM), f2(cf0)));
+            A[r][q] = __ffma2_rn(rr[q], f2(cf1), __ffma2_rn(A[r][q], f2(kM), f2(cf0)));
             X[r][q] = __ffma2_rn(A[r][q], f2(kC), __fmul2_rn(X[r][q], f2(kM)));
           }
         }
@@ -305,10 +313,19 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
         const float sim = red_sub<LD>(acc.x + acc.y + cj);
         const float2 sim_s = f2(sim * sT), simg = f2(sim * cds);
         float2 gacc = f2(0.0f);
+        float2 tsv[KP], rrv[KP];
+#pragma unroll
+        for (int q = 0; q < KP; ++q) tsv[q] = __ffma2_rn(sim_s, xj[q], __fmul2_rn(X[r][q], alpha_s));
+        if constexpr (KP >= 2 && NCN_FEAT_BWD_BATCH > 1) {
+          act_r_all<ACT, KP, NCN_FEAT_BWD_BATCH>(tsv, rrv);
+        } else {
+#pragma unroll
+          for (int q = 0; q < KP; ++q) rrv[q] = F::r(tsv[q]);
+        }
 #pragma unroll
         for (int q = 0; q < KP; ++q) {
-          const float2 ts = __ffma2_rn(sim_s, xj[q], __fmul2_rn(X[r][q], alpha_s));
-          const float2 rr = F::r(ts);
+          const float2 ts = tsv[q];
+          const float2 rr = rrv[q];
           A[r][q] = __ffma2_rn(rr, f2(af1), __ffma2_rn(A[r][q], f2(kInvM), f2(af0)));
           const float2 gap = __ffma2_rn(f2(kC), H[r][q], Gv[r][q]);
           const float2 gt = F::gt(gap, ts, rr);
