@@ -75,6 +75,24 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
                   int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation, int dtype,
                   void* stream);
 
+/* One stage with a context length per batch row, forward and backward.  Replace the step-count rule of the
+ * reference's earlier Triton operator (ncn_triton/ncn_triton_old.py:70-96 forward, :186-197 backward:
+ * `ctxlen = load(ctxlen_tensor + batch)`, `hi = GROUP if group*GROUP + GROUP < ctxlen else ctxlen - group*GROUP`,
+ * steps 0 .. hi-1), applied to the stage index map of torch_ref/ncn_pytorch.py:12-41.
+ * ctxlen: int32 [B] on the device.  Group g of row b counts its members g*n_cache .. g*n_cache+n_cache-1 against
+ * ctxlen[b]: groups before it take all n_cache steps, the group it cuts takes the steps of the members before
+ * it, groups at or beyond it take none.  Every position is still read and written: positions of groups that
+ * take no step pass through unchanged (y = x, ya = xa; dx = dy, dxa = dya) - the reference leaves them
+ * unwritten.  ctxlen[b] >= N gives ncn_stage_fwd / ncn_stage_bwd.  Other arguments as in those calls; these
+ * entries always run the shared-memory kernels (any E, n_head, n_cache). */
+int ncn_stage_fwd_ctx(const void* x, const void* xa, const float* W, const int* ctxlen, void* y, void* ya, int64_t B,
+                      int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation, int dtype,
+                      void* stream);
+int ncn_stage_bwd_ctx(const void* y, const void* ya, const void* dy, const void* dya, const float* W, const int* ctxlen,
+                      void* dx, void* dxa, void* x_rec, void* xa_rec, float* dW, void* workspace, size_t workspace_bytes,
+                      int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                      int dtype, void* stream);
+
 /* All L stages (module_l = first_module .. first_module+L-1) in one kernel.  Replaces the stage
  * loops NCNNetCuda.forward / NCNNetTestCuda.forward (ncn_pytorch_wrapper_v2.py:114-117,132-144).
  * ckpt (may be null without NCN_TAPE): fp32 buffer of ncn_ckpt_bytes(...) bytes that receives the state

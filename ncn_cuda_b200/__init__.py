@@ -8,11 +8,13 @@ from . import ops
 from .ncn_pytorch import RefTorchNaive, group_pos_to_index_v2, ref_naive_fwd
 from .ncn_pytorch_invertible import NCNFunctionPytorch, RefInvTorchNaive
 from .ncn_pytorch_wrapper_v2 import (
+    NCNContextFunction,
     NCNFunction,
     NCNModuleCuda,
     NCNNetCuda,
     NCNNetFunction,
     NCNNetTestCuda,
+    fused_ncn_cuda_ctxlen,
     fused_ncn_cuda_v2,
     fused_ncn_net,
 )
@@ -21,5 +23,6 @@ from .stack import NCNResidualStack, allreduce_weight_grads, shard_rows
 __all__ = [
     "ops", "NCNFunction", "NCNNetFunction", "fused_ncn_cuda_v2", "fused_ncn_net", "NCNModuleCuda", "NCNNetCuda",
     "NCNNetTestCuda", "RefTorchNaive", "ref_naive_fwd", "group_pos_to_index_v2", "NCNFunctionPytorch",
-    "RefInvTorchNaive", "NCNResidualStack", "allreduce_weight_grads", "shard_rows",
+    "RefInvTorchNaive", "NCNResidualStack", "allreduce_weight_grads", "shard_rows", "NCNContextFunction",
+    "fused_ncn_cuda_ctxlen",
 ]

@@ -751,6 +751,60 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
   return NCN_OK;
 }
 
+// ---- per-stage launches of the shared-memory kernels (any E, heads, n_cache; optional per-row context length)
+static int stage_fwd_generic(const void* x, const void* xa, const float* W, const int* ctxlen, void* y, void* ya, int64_t B,
+                             int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                             int dtype, const DevInfo& dev, void* stream) {
+  StageParams p{};
+  fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
+  p.in[0] = x; p.in[1] = xa;
+  p.out[0] = y; p.out[1] = ya;
+  p.W = W;
+  p.ctxlen = ctxlen;
+  GenericPlan g;
+  int rc;
+  const int act = map_act(activation);
+  if (dtype == DT_BF16) {
+    if ((rc = plan_generic(stage_fwd_kernel<__nv_bfloat16>, false, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_fwd_kernel<__nv_bfloat16><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  } else {
+    if ((rc = plan_generic(stage_fwd_kernel<float>, false, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_fwd_kernel<float><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? NCN_OK : cuda_fail(e);
+}
+
+static int stage_bwd_generic(const void* y, const void* ya, const void* dy, const void* dya, const float* W,
+                             const int* ctxlen, void* dx, void* dxa, void* x_rec, void* xa_rec, float* dW, float* partials,
+                             int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha,
+                             int activation, int dtype, const DevInfo& dev, void* stream) {
+  StageParams p{};
+  fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
+  p.in[0] = y; p.in[1] = ya; p.in[2] = dy; p.in[3] = dya;
+  p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
+  p.W = W;
+  p.ctxlen = ctxlen;
+  p.partials = partials;
+  GenericPlan g;
+  int rc;
+  const int act = map_act(activation);
+  if (dtype == DT_BF16) {
+    if ((rc = plan_generic(stage_bwd_kernel<__nv_bfloat16>, true, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_bwd_kernel<__nv_bfloat16><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  } else {
+    if ((rc = plan_generic(stage_bwd_kernel<float>, true, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
+    p.warps = g.warps; p.warp_floats = g.warp_floats;
+    stage_bwd_kernel<float><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return reduce_dw(p.partials, dW, g.grid, 2 * (int)E, 0, (cudaStream_t)stream);
+}
+
 static size_t workspace_floats(const DevInfo& dev, int64_t E, int L) {
   return (size_t)dev.sms * 32 * 2 * (size_t)E * (size_t)(L < 1 ? 1 : L);
 }
@@ -1001,24 +1055,8 @@ int ncn_stage_fwd(const void* x, const void* xa, const float* W, void* y, void* 
                      (cudaStream_t)stream, nullptr);
     if (rc != NCN_ERR_UNSUPPORTED) return rc;
   }
-  StageParams p{};
-  fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
-  p.in[0] = x; p.in[1] = xa;
-  p.out[0] = y; p.out[1] = ya;
-  p.W = W;
-  GenericPlan g;
-  const int act = map_act(activation);
-  if (dtype == DT_BF16) {
-    if ((rc = plan_generic(stage_fwd_kernel<__nv_bfloat16>, false, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
-    p.warps = g.warps; p.warp_floats = g.warp_floats;
-    stage_fwd_kernel<__nv_bfloat16><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
-  } else {
-    if ((rc = plan_generic(stage_fwd_kernel<float>, false, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
-    p.warps = g.warps; p.warp_floats = g.warp_floats;
-    stage_fwd_kernel<float><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
-  }
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? NCN_OK : cuda_fail(e);
+  return stage_fwd_generic(x, xa, W, nullptr, y, ya, B, N, E, n_cache, n_head, module_l, alpha, activation, dtype, dev,
+                           stream);
 }
 
 int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya, const float* W, void* dx, void* dxa,
@@ -1048,26 +1086,37 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
     if (rc == NCN_OK) return reduce_dw(static_cast<float*>(workspace), dW, fgrid, 2 * (int)E, 0, (cudaStream_t)stream);
     if (rc != NCN_ERR_UNSUPPORTED) return rc;
   }
-  StageParams p{};
-  fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
-  p.in[0] = y; p.in[1] = ya; p.in[2] = dy; p.in[3] = dya;
-  p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
-  p.W = W;
-  p.partials = static_cast<float*>(workspace);
-  GenericPlan g;
-  const int act = map_act(activation);
-  if (dtype == DT_BF16) {
-    if ((rc = plan_generic(stage_bwd_kernel<__nv_bfloat16>, true, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
-    p.warps = g.warps; p.warp_floats = g.warp_floats;
-    stage_bwd_kernel<__nv_bfloat16><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
-  } else {
-    if ((rc = plan_generic(stage_bwd_kernel<float>, true, p.groups, p.n, p.d, p.E, dev, g)) != NCN_OK) return rc;
-    p.warps = g.warps; p.warp_floats = g.warp_floats;
-    stage_bwd_kernel<float><<<g.grid, g.warps * 32, g.smem, (cudaStream_t)stream>>>(p, act);
-  }
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e);
-  return reduce_dw(p.partials, dW, g.grid, 2 * (int)E, 0, (cudaStream_t)stream);
+  return stage_bwd_generic(y, ya, dy, dya, W, nullptr, dx, dxa, x_rec, xa_rec, dW, static_cast<float*>(workspace), B, N, E,
+                           n_cache, n_head, module_l, alpha, activation, dtype, dev, stream);
+}
+
+int ncn_stage_fwd_ctx(const void* x, const void* xa, const float* W, const int* ctxlen, void* y, void* ya, int64_t B,
+                      int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation, int dtype,
+                      void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!x || !xa || !W || !ctxlen || !y || !ya) return NCN_ERR_NULL;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  return stage_fwd_generic(x, xa, W, ctxlen, y, ya, B, N, E, n_cache, n_head, module_l, alpha, activation, dtype, dev,
+                           stream);
+}
+
+int ncn_stage_bwd_ctx(const void* y, const void* ya, const void* dy, const void* dya, const float* W, const int* ctxlen,
+                      void* dx, void* dxa, void* x_rec, void* xa_rec, float* dW, void* workspace, size_t workspace_bytes,
+                      int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                      int dtype, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!y || !ya || !dy || !dya || !W || !ctxlen || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  if (!workspace || workspace_bytes < workspace_floats(dev, E, 1) * sizeof(float)) return NCN_ERR_WORKSPACE;
+  return stage_bwd_generic(y, ya, dy, dya, W, ctxlen, dx, dxa, x_rec, xa_rec, dW, static_cast<float*>(workspace), B, N, E,
+                           n_cache, n_head, module_l, alpha, activation, dtype, dev, stream);
 }
 
 }  // extern "C"

@@ -17,6 +17,7 @@ struct StageParams {
   void* out[4];       // fwd: y, ya ; bwd: dx, dxa, x_rec|null, xa_rec|null
   const float* W;     // [2E]
   float* partials;    // bwd: [gridDim.x][2E]
+  const int* ctxlen;  // [B] context length per batch row, or null: every group takes all n steps
   long long B;
   long long groups;   // B * C * m
   int N, E, C, d, n, m, stride, ld_shift;  // LD = 1 << ld_shift
@@ -47,6 +48,16 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// Steps group g of row b takes.  With per-row context lengths (the reference's earlier Triton kernels,
+// ncn_triton/ncn_triton_old.py:91-96, 189-192) a group counts its members g*n .. g*n+n-1 against the
+// row's length: groups that lie before it take all n steps, the group it cuts takes the steps of the
+// members before it, groups beyond it take none (their positions pass through unchanged).
+__device__ __forceinline__ int group_steps(const int* ctxlen, long long b, int g, int n) {
+  if (ctxlen == nullptr) return n;
+  const long long left = (long long)ctxlen[b] - (long long)g * n;
+  return left <= 0 ? 0 : (left < n ? (int)left : n);
 }
 
 // element offset of (row b, position pos, feature f)
@@ -86,7 +97,8 @@ __global__ void __launch_bounds__(256) stage_fwd_kernel(const StageParams p, con
       }
     }
     __syncwarp();
-    for (int j = 0; j < n; ++j) {
+    const int steps = group_steps(p.ctxlen, b, g, n);
+    for (int j = 0; j < steps; ++j) {
       float cj = 0.0f;
       for (int k = lane; k < d; k += 32) {
         const float v = X[j * pitch + k];
@@ -174,7 +186,7 @@ __global__ void __launch_bounds__(256) stage_bwd_kernel(const StageParams p, con
       }
     }
     __syncwarp();
-    for (int j = n - 1; j >= 0; --j) {
+    for (int j = group_steps(p.ctxlen, b, g, n) - 1; j >= 0; --j) {
       // x = (y - c ya) / m
       for (int i = li; i < n; i += LT)
         for (int k = lk; k < d; k += LD) X[i * pitch + k] = fmaf(A[i * pitch + k], -kCoverM, X[i * pitch + k] * kInvM);

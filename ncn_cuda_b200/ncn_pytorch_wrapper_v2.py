@@ -67,6 +67,31 @@ def fused_ncn_cuda_v2(
     return yi, ya
 
 
+class NCNContextFunction(torch.autograd.Function):
+    """One stage with a context length per batch row: the step-count rule of the reference's earlier
+    Triton operator (ncn_triton/ncn_triton_old.py:285-359 `FusedLinearChunkNCNFunction`, kernels
+    :52-124, :141-283) on the stage index map of torch_ref.  Saves the stage output, like NCNFunction."""
+
+    @staticmethod
+    def forward(ctx, x, xa, W, ctxlen, alpha, activation, n_cache, n_head, module_l):
+        yi, ya = ops.stage_fwd_ctx(x, xa, W, ctxlen, alpha, activation, n_cache, n_head, module_l)
+        ctx.save_for_backward(yi, ya, W, torch.as_tensor(ctxlen).to(device=x.device, dtype=torch.int32))
+        ctx.cfg = (alpha, activation, n_cache, n_head, module_l)
+        return yi, ya
+
+    @staticmethod
+    def backward(ctx, dyi, dya):
+        yi, ya, W, ctxlen = ctx.saved_tensors
+        alpha, activation, n_cache, n_head, module_l = ctx.cfg
+        dx, dxa, dW = ops.stage_bwd_ctx(yi, ya, dyi, dya, W, ctxlen, alpha, activation, n_cache, n_head, module_l)
+        return dx, dxa, dW.to(W.dtype), None, None, None, None, None, None
+
+
+def fused_ncn_cuda_ctxlen(x, xa, W, ctxlen, alpha, activation, n_cache, n_head, module_l):
+    """fused_ncn_cuda_v2 with a context length per batch row (int tensor [B])."""
+    return NCNContextFunction.apply(x, xa, W, ctxlen, alpha, activation, n_cache, n_head, module_l)
+
+
 def plan_backward(dtype, n_cache: int, num_modules: int, residual: bool, backward_mode: str):
     """-> (recompute, ckpt_every, tape) for a fused net.
 

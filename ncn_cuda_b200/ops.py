@@ -115,6 +115,54 @@ def stage_bwd(y, ya, dy, dya, W, alpha, activation, n_cache, n_head, module_l, w
     return dx, dxa, dW
 
 
+def _ctxlen(ctxlen, B, device) -> torch.Tensor:
+    ctxlen = torch.as_tensor(ctxlen)
+    if ctxlen.numel() != B:
+        raise ValueError(f"ctxlen has {ctxlen.numel()} entries for {B} batch rows")
+    return ctxlen.to(device=device, dtype=torch.int32).contiguous()
+
+
+def stage_fwd_ctx(x, xa, W, ctxlen, alpha, activation, n_cache, n_head, module_l) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One stage with a context length per batch row (ncn_stage_fwd_ctx): group g of row b takes
+    min(n_cache, max(0, ctxlen[b] - g * n_cache)) steps."""
+    lib = _lib.load()
+    _check_inputs(x, xa)
+    x, xa = x.contiguous(), xa.contiguous()
+    B, N, E = x.shape
+    W = _weights(W, 2 * E, x.device)
+    cl = _ctxlen(ctxlen, B, x.device)
+    y, ya = torch.empty_like(x), torch.empty_like(xa)
+    with torch.cuda.device(x.device):
+        rc = lib.ncn_stage_fwd_ctx(
+            x.data_ptr(), xa.data_ptr(), W.data_ptr(), cl.data_ptr(), y.data_ptr(), ya.data_ptr(), B, N, E, n_cache, n_head,
+            module_l, float(alpha), activation_code(activation), _dtype_code(x), _stream(),
+        )
+    _lib.check("ncn_stage_fwd_ctx", rc)
+    return y, ya
+
+
+def stage_bwd_ctx(y, ya, dy, dya, W, ctxlen, alpha, activation, n_cache, n_head, module_l):
+    """Backward of stage_fwd_ctx from the stage output.  Returns (dx, dxa, dW[2E])."""
+    lib = _lib.load()
+    _check_inputs(y, ya, dy, dya)
+    y, ya, dy, dya = y.contiguous(), ya.contiguous(), dy.contiguous(), dya.contiguous()
+    B, N, E = y.shape
+    W = _weights(W, 2 * E, y.device)
+    cl = _ctxlen(ctxlen, B, y.device)
+    dx, dxa = torch.empty_like(y), torch.empty_like(y)
+    dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
+    dt = _dtype_code(y)
+    with torch.cuda.device(y.device):
+        ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
+        rc = lib.ncn_stage_bwd_ctx(
+            y.data_ptr(), ya.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(), cl.data_ptr(), dx.data_ptr(),
+            dxa.data_ptr(), None, None, dW.data_ptr(), ws.data_ptr(), ws.numel(), B, N, E, n_cache, n_head, module_l,
+            float(alpha), activation_code(activation), dt, _stream(),
+        )
+    _lib.check("ncn_stage_bwd_ctx", rc)
+    return dx, dxa, dW
+
+
 def net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, ckpt_every=0, residual=False, tape=False):
     """All stages in one kernel.  W: [L, 2E].  Returns (y, ya, ckpt or None).  ckpt holds the fp32
     state after every ckpt_every-th stage and, with tape, after the last one."""

@@ -449,3 +449,36 @@ def test_host_buffer_pipeline(ncn, dtype, tol):
     # same call again: bitwise identical (fixed chunk order)
     y2, ya2, dx2, dxa2, dW2 = net_fwd_bwd_host(host[0], host[1], W, host[2], host[3], 0.9, "tanh", n, 1, chunk_rows=16)
     assert torch.equal(dW, dW2) and torch.equal(dx, dx2)
+
+
+# ---------------------------------------------------------------- context length per batch row
+@pytest.mark.parametrize("B,N,E,C,n,l,act,lens", [
+    (5, 64, 1, 1, 4, 0, "tanh", [64, 61, 17, 4, 0]),        # full, cut inside the last group, mid, one group, nothing
+    (4, 96, 8, 2, 8, 2, "tanh", [96, 50, 9, 95]),           # several features, a stage with stride 2 (m = 12)
+    (3, 128, 16, 4, 32, 1, "linear", [128, 33, 100]),       # the reference's group size
+    (3, 40, 6, 3, 5, 3, "relu", [40, 12, 38]),              # n = 5, m = 8
+])
+def test_stage_context_length(ncn, B, N, E, C, n, l, act, lens):
+    torch.manual_seed(N + E)
+    x, xa = torch.randn(B, N, E), torch.randn(B, N, E) * 0.3
+    W = torch.randn(2 * E) * (0.5 / E ** 0.5)
+    dy, dya = torch.randn(B, N, E), torch.randn(B, N, E)
+    ctx = torch.tensor(lens, dtype=torch.int32)
+    code = ncn.ops.ACTIVATION_CODES[act]
+    xd, xad, Wd = dev(x).requires_grad_(), dev(xa).requires_grad_(), dev(W).requires_grad_()
+    y, ya = ncn.fused_ncn_cuda_ctxlen(xd, xad, Wd, ctx, 0.9, code, n, C, l)
+    torch.autograd.backward([y, ya], [dev(dy), dev(dya)])
+    ncn.ops.device_status()
+    xr, xar, Wr = x.clone().requires_grad_(), xa.clone().requires_grad_(), W.clone().requires_grad_()
+    ry, rya = O.stage_forward_ctxlen(xr, xar, Wr, ctx, 0.9, act, n, C, l)
+    torch.autograd.backward([ry, rya], [dy, dya])
+    tol = 3e-5 if n >= 32 else TOL32
+    assert_close((y.detach(), ya.detach(), xd.grad, xad.grad, [Wd.grad]), (ry.detach(), rya.detach(), xr.grad, xar.grad, [Wr.grad]), tol)
+    # a full-length row equals the plain operator; a row of length 0 passes through
+    full = [b for b, c in enumerate(lens) if c >= N]
+    if full:
+        py, pya = ncn.ops.stage_fwd(dev(x), dev(xa), dev(W), 0.9, code, n, C, l)
+        assert O.rel_err(y[full], py[full]) < 2e-6 and O.rel_err(ya[full], pya[full]) < 2e-6
+    for b, c in enumerate(lens):
+        if c == 0:
+            assert torch.equal(y[b].cpu(), x[b]) and torch.equal(xd.grad[b].cpu(), dy[b])
