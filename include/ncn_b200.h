@@ -11,7 +11,9 @@
  *    `dtype` (NCN_F32 or NCN_BF16); weights and weight gradients are always fp32;
  *  - W of one stage is [2E] = [Wi | Wj] (torch_ref/ncn_pytorch.py:60-61); W of a net is [L][2E];
  *  - activation codes are the reference's (ncn_pytorch_wrapper_v2.py:111):
- *    0 tanh, 1 relu, 2 sigmoid, anything else (-1) linear;
+ *    0 tanh, 1 relu, 2 sigmoid, anything else (-1) linear; 3 is added for "leaky-relu" (slope 0.01,
+ *    torch_ref/ncn_pytorch_invertible.py:39-44, ncn_triton/ncn_triton.py:22-28), which the per-stage
+ *    calls run on their general kernels and the net calls answer with NCN_ERR_UNSUPPORTED;
  *  - the caller owns every buffer; nothing is allocated, freed or memset by the library
  *    (unless a function says otherwise); every output element is written exactly once;
  *  - work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns without

@@ -99,6 +99,7 @@ static int map_act(int code) {
     case 0: return ACT_TANH;
     case 1: return ACT_RELU;
     case 2: return ACT_SIGMOID;
+    case 3: return ACT_LEAKY;  // shared-memory stage kernels only
     default: return ACT_LINEAR;
   }
 }
@@ -710,7 +711,7 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
   const int d = (int)(E / C);
   const int gpw = feat_groups_per_warp(n, d);
   FeatLaunchFn fn = feat_fn(n, bwd);
-  if (gpw == 0 || fn == nullptr) return NCN_ERR_UNSUPPORTED;
+  if (gpw == 0 || fn == nullptr || map_act(activation) == ACT_LEAKY) return NCN_ERR_UNSUPPORTED;
   if (env_switches().no_feat) return NCN_ERR_UNSUPPORTED;  // tuning experiments: force the shared-memory kernels
   const int act = fused_act(map_act(activation), dtype);
   for (int q = 0; q < (bwd ? 4 : 2); ++q)
@@ -899,7 +900,7 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
   if (L < 1 || first_module < 0) return NCN_ERR_SHAPE;
   if (!x || !xa || !W || !y || !ya) return NCN_ERR_NULL;
   if ((flags & F_TAPE) && !ckpt) return NCN_ERR_NULL;
-  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
+  if (!rows_shape_ok(N, E, n_cache, n_head, dtype) || map_act(activation) == ACT_LEAKY) return NCN_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(xa) || !aligned16(y) || !aligned16(ya) || (ckpt && !aligned16(ckpt)))
     return NCN_ERR_ALIGN;
   DevInfo dev;
@@ -965,7 +966,7 @@ static int net_bwd_impl(const void* s0, const void* s1, const void* dy, const vo
   if (tape && (flags & F_RECOMPUTE)) return NCN_ERR_UNSUPPORTED;
   if ((!tape && (!s0 || !s1)) || (tape && !ckpt) || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
   if ((x_rec == nullptr) != (xa_rec == nullptr)) return NCN_ERR_NULL;
-  if (!rows_shape_ok(N, E, n_cache, n_head, dtype)) return NCN_ERR_UNSUPPORTED;
+  if (!rows_shape_ok(N, E, n_cache, n_head, dtype) || map_act(activation) == ACT_LEAKY) return NCN_ERR_UNSUPPORTED;
   if ((flags & F_RESIDUAL) && !(flags & (F_RECOMPUTE | F_TAPE))) return NCN_ERR_UNSUPPORTED;
   if (!aligned16(s0) || !aligned16(s1) || !aligned16(dy) || !aligned16(dya) || !aligned16(dx) || !aligned16(dxa) ||
       (x_rec && (!aligned16(x_rec) || !aligned16(xa_rec))) || (ckpt && !aligned16(ckpt)))
@@ -1044,7 +1045,7 @@ int ncn_stage_fwd(const void* x, const void* xa, const float* W, void* y, void* 
   if (rows_shape_ok(N, E, n_cache, n_head, dtype) && aligned16(x) && aligned16(xa) && aligned16(y) && aligned16(ya)) {
     rc = ncn_net_fwd(x, xa, W, y, ya, nullptr, 0, B, N, E, n_cache, n_head, module_l, 1, alpha, activation, dtype, 0,
                      stream);
-    if (rc != NCN_ERR_SMEM) return rc;
+    if (rc != NCN_ERR_SMEM && rc != NCN_ERR_UNSUPPORTED) return rc;
   }
   DevInfo dev;
   if ((rc = get_dev(dev)) != NCN_OK) return rc;
@@ -1075,7 +1076,7 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
       aligned16(dx) && aligned16(dxa) && (!x_rec || (aligned16(x_rec) && aligned16(xa_rec)))) {
     rc = ncn_net_bwd(y, ya, dy, dya, W, dx, dxa, x_rec, xa_rec, dW, nullptr, 0, workspace, workspace_bytes, B, N, E,
                      n_cache, n_head, module_l, 1, alpha, activation, dtype, 0, 0, stream);
-    if (rc != NCN_ERR_SMEM) return rc;
+    if (rc != NCN_ERR_SMEM && rc != NCN_ERR_UNSUPPORTED) return rc;
   }
   {
     const void* fin[4] = {y, ya, dy, dya};

@@ -3,7 +3,8 @@
 // The math follows the reference's torch implementation:
 //   stage index map   torch_ref/ncn_pytorch.py:12-41
 //   recurrence step   torch_ref/ncn_pytorch.py:74-94
-//   activation codes  ncn_cuda/ncn_pytorch_wrapper_v2.py:111  (0 tanh, 1 relu, 2 sigmoid, else linear)
+//   activation codes  ncn_cuda/ncn_pytorch_wrapper_v2.py:111  (0 tanh, 1 relu, 2 sigmoid, else linear);
+//                     3 = leaky-relu, slope 0.01 (torch_ref/ncn_pytorch_invertible.py:39-44, ncn_triton/ncn_triton.py:22-28)
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -20,7 +21,8 @@ constexpr float kCoverM = 0.1f / 0.9f;
 
 // ACT_TANH_FAST is internal: tanh through the one-instruction tanh.approx.f32 (relative error 2^-11),
 // used for bf16 storage, whose 2e-2 tolerance it does not threaten; it halves the special-function work.
-enum Act : int { ACT_TANH = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_LINEAR = 3, ACT_TANH_FAST = 4 };
+// ACT_LEAKY runs on the shared-memory stage kernels only (ncn_generic.cuh).
+enum Act : int { ACT_TANH = 0, ACT_RELU = 1, ACT_SIGMOID = 2, ACT_LINEAR = 3, ACT_TANH_FAST = 4, ACT_LEAKY = 5 };
 enum DType : int { DT_F32 = 0, DT_BF16 = 1 };
 
 // flags of the fused row kernels
@@ -211,6 +213,8 @@ __device__ __forceinline__ float act_fwd(float t) {
   } else if constexpr (ACT == ACT_SIGMOID) {
     float e = ex2_approx(t * -1.4426950408889634f);
     return rcp_approx(e + 1.0f);
+  } else if constexpr (ACT == ACT_LEAKY) {
+    return t >= 0.0f ? t : 0.01f * t;
   } else {
     return t;
   }
@@ -223,6 +227,8 @@ __device__ __forceinline__ float act_grad(float t, float f) {
     return t > 0.0f ? 1.0f : 0.0f;
   } else if constexpr (ACT == ACT_SIGMOID) {
     return f * (1.0f - f);
+  } else if constexpr (ACT == ACT_LEAKY) {
+    return t >= 0.0f ? 1.0f : 0.01f;
   } else {
     return 1.0f;
   }

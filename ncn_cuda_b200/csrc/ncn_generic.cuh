@@ -32,6 +32,7 @@ __device__ __forceinline__ float act_rt(int act, float t) {
     case ACT_TANH: return act_fwd<ACT_TANH>(t);
     case ACT_RELU: return act_fwd<ACT_RELU>(t);
     case ACT_SIGMOID: return act_fwd<ACT_SIGMOID>(t);
+    case ACT_LEAKY: return act_fwd<ACT_LEAKY>(t);
     default: return t;
   }
 }
@@ -40,6 +41,7 @@ __device__ __forceinline__ float act_grad_rt(int act, float t, float f) {
     case ACT_TANH: return act_grad<ACT_TANH>(t, f);
     case ACT_RELU: return act_grad<ACT_RELU>(t, f);
     case ACT_SIGMOID: return act_grad<ACT_SIGMOID>(t, f);
+    case ACT_LEAKY: return act_grad<ACT_LEAKY>(t, f);
     default: return 1.0f;
   }
 }

@@ -4,8 +4,10 @@
 `RefInvTorchNaive` (:302-358) the stack built on it.  Here the backward really is the
 reversible one: only outputs are kept and the step inputs are rebuilt by the inverse of
 :87-113 inside the kernels (the reference keeps per-step copies instead, :131-132).
-Activation vocabulary of that file (:39-44): "tanh", anything else linear; "leaky-relu"
-raises, as it does in the reference (torch has no `torch.leaky_relu`).
+Activation vocabulary of that file (:39-44): "leaky-relu", "tanh", anything else linear.  In the
+reference the "leaky-relu" branch calls `torch.leaky_relu`, which torch does not have, so it cannot
+run there; here it is the function the reference's Triton path defines (ncn_triton/ncn_triton.py:22-28,
+slope 0.01).
 """
 from __future__ import annotations
 
@@ -18,7 +20,7 @@ from .ncn_pytorch_wrapper_v2 import _net_forward
 
 def _activation_nr(activation) -> int:
     if activation == "leaky-relu":
-        raise AttributeError("'leaky-relu' is not runnable in the reference (no torch.leaky_relu); not provided")
+        return ops.ACTIVATION_CODES["leaky-relu"]
     return ops.ACTIVATION_CODES["tanh"] if activation == "tanh" else ops.ACTIVATION_CODES["linear"]
 
 

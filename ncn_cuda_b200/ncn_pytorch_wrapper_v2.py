@@ -173,7 +173,7 @@ def _net_forward(x, xa, weights: Sequence[torch.Tensor], alpha, activation_nr, n
     """Shared by the two net modules: fused when the library covers the shape, else stage by stage."""
     L = len(weights)
     fused = False
-    if L > 0 and x.is_cuda:
+    if L > 0 and x.is_cuda and ops.activation_code(activation_nr) != ops.LEAKY_RELU:  # leaky-relu: per-stage kernels
         recompute, every, tape = plan_backward(x.dtype, n_cache, L, False, backward_mode)
         flags = (ops.NCN_RECOMPUTE if recompute else 0) | (ops.NCN_TAPE if tape else 0)
         fused = ops.net_supported(x, n_cache, n_head, L, flags, every)

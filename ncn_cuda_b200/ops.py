@@ -12,8 +12,10 @@ import torch
 from . import _lib
 from ._lib import NCN_BF16, NCN_F32, NCN_RECOMPUTE, NCN_RESIDUAL, NCN_TAPE
 
-# activation vocabulary of the reference's CUDA wrapper (ncn_cuda/ncn_pytorch_wrapper_v2.py:111)
-ACTIVATION_CODES = {"tanh": 0, "relu": 1, "sigmoid": 2, "linear": -1}
+# activation vocabulary of the reference's CUDA wrapper (ncn_cuda/ncn_pytorch_wrapper_v2.py:111), plus the
+# "leaky-relu" of its torch_ref-invertible and Triton paths (per-stage kernels only)
+ACTIVATION_CODES = {"tanh": 0, "relu": 1, "sigmoid": 2, "linear": -1, "leaky-relu": 3}
+LEAKY_RELU = 3
 
 _workspaces = {}
 

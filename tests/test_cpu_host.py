@@ -107,13 +107,12 @@ def test_index_map_matches_oracle():
 def test_activation_vocabulary():
     from ncn_cuda_b200 import ops
 
-    assert ops.ACTIVATION_CODES == {"tanh": 0, "relu": 1, "sigmoid": 2, "linear": -1}
+    assert ops.ACTIVATION_CODES == {"tanh": 0, "relu": 1, "sigmoid": 2, "linear": -1, "leaky-relu": 3}
     assert ops.activation_code("linear") == -1 and ops.activation_code(2) == 2
     from ncn_cuda_b200.ncn_pytorch_invertible import _activation_nr
 
     assert _activation_nr("tanh") == 0 and _activation_nr("anything") == -1
-    with pytest.raises(AttributeError):
-        _activation_nr("leaky-relu")
+    assert _activation_nr("leaky-relu") == 3
 
 
 WORKER = r"""

@@ -97,6 +97,8 @@ STAGE_CASES = [
     (1, 64, 128, 4, 32, 1, "tanh"),
     (2, 32, 40, 1, 8, 3, "linear"),    # d = 40 > 32
     (5, 30, 1, 1, 2, 3, "tanh"),       # N % 4 != 0: generic kernel
+    (3, 64, 1, 1, 4, 2, "leaky-relu"),  # general kernels (one feature per position)
+    (2, 64, 32, 4, 8, 1, "leaky-relu"), # general kernels (several features)
 ]
 
 
@@ -252,6 +254,7 @@ NET_CASES = [
     (3, 12, 2, 4, 0.3, "tanh"),       # m = 6, n = 2
     (1, 8, 4, 2, 0.3, "tanh"),        # one row of two groups: a single pair
     (1030, 256, 8, 3, 0.1, "tanh"),   # several tiles per CTA with a ragged last one
+    (6, 256, 4, 4, 0.25, "leaky-relu"),  # no fused kernels for this activation: stage by stage
 ]
 
 
