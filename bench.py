@@ -43,8 +43,12 @@ WORKLOADS = {
                  desc="bf16 storage x[262144,8192] g=16 4 stages"),
     "cfg5": dict(B=131072, N=2048, n=8, L=4, w_var=1 / 8, dtype="bf16", act="tanh", seed=4, layers=12, mode="tape",
                  desc="12 residual NCN layers D=2048 g=8 4 stages bf16, 131072 rows per GPU (1/8 of the 8-GPU global batch)"),
-    "ref_e128": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
-                     desc="the reference's own bench shape scaled in rows: x[4096,256,128] 4 heads g=32 3 stages, one kernel per stage"),
+    "ref_e128": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5, stage_keep="output",
+                     desc="the reference's own bench shape scaled in rows: x[4096,256,128] 4 heads g=32 3 stages, one kernel per "
+                          "stage, backward from each stage's output alone (the reference operator's contract)"),
+    "ref_e128_input": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
+                           stage_keep="input",
+                           desc="ref_e128 with the stage inputs kept for the backward (inverse chains of 16 steps: 1e-5 gradients)"),
     "ref_e128_small": dict(B=1024, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
                            desc="ref_e128 with 1024 rows (profiling case)"),
     "small": dict(B=8192, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="tanh", seed=1,
@@ -252,6 +256,9 @@ def measure(ncn, name, wl, mode_override, dev, rank, world, steps, warmup, clock
         ws = [(torch.randn(2 * E, generator=gw) * wl["w_var"] ** 0.5).to(dev).requires_grad_(True) for _ in range(L)]
         net = ncn.NCNNetTestCuda(0.9, wl["act"], n, C, L, ws, backward_mode=mode)
 
+    if wl.get("stage_keep"):
+        ncn.set_stage_backward(wl["stage_keep"])  # per-stage operator: what it keeps for its backward
+
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
 
     def step(i=None):
@@ -285,6 +292,7 @@ def measure(ncn, name, wl, mode_override, dev, rank, world, steps, warmup, clock
         dist.barrier()
     torch.cuda.synchronize()
     ncn.ops.device_status()
+    ncn.set_stage_backward("auto")
     ms = t_start.elapsed_time(t_end)
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)

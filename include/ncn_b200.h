@@ -77,6 +77,19 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
                   int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation, int dtype,
                   void* stream);
 
+/* ncn_stage_bwd for callers that also kept the stage INPUT (x, xa).  No counterpart in the reference, whose
+ * NCNFunction saves the stage output only (ncn_cuda/ncn_pytorch_wrapper_v2.py:21, 35) and rebuilds the input by
+ * the inverse of torch_ref/ncn_pytorch_invertible.py:97-111: every rebuilt step divides by 0.9, so a stage of
+ * n_cache = 32 steps leaves fp32 gradients at about 1e-5 of their size.  Here the state at every 16th step is
+ * rebuilt exactly by running the forward from the saved input, so no inverse chain exceeds 16 steps and the
+ * gradients keep the accuracy of plain autograd.  With bf16 storage the whole stage is replayed from the input
+ * (y, ya are not read and may be null): an inverse started from rounded outputs would amplify their rounding.
+ * With fp32 storage and n_cache <= 16 this is ncn_stage_bwd (x, xa are not read).  Results as ncn_stage_bwd. */
+int ncn_stage_bwd_saved(const void* x, const void* xa, const void* y, const void* ya, const void* dy, const void* dya,
+                        const float* W, void* dx, void* dxa, float* dW, void* workspace, size_t workspace_bytes, int64_t B,
+                        int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                        int dtype, void* stream);
+
 /* One stage with a context length per batch row, forward and backward.  Replace the step-count rule of the
  * reference's earlier Triton operator (ncn_triton/ncn_triton_old.py:70-96 forward, :186-197 backward:
  * `ctxlen = load(ctxlen_tensor + batch)`, `hi = GROUP if group*GROUP + GROUP < ctxlen else ctxlen - group*GROUP`,

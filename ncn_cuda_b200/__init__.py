@@ -15,6 +15,7 @@ from .ncn_pytorch_wrapper_v2 import (
     NCNNetFunction,
     NCNNetTestCuda,
     fused_ncn_cuda_ctxlen,
+    set_stage_backward,
     fused_ncn_cuda_v2,
     fused_ncn_net,
 )
@@ -25,4 +26,5 @@ __all__ = [
     "NCNNetTestCuda", "RefTorchNaive", "ref_naive_fwd", "group_pos_to_index_v2", "NCNFunctionPytorch",
     "RefInvTorchNaive", "NCNResidualStack", "allreduce_weight_grads", "shard_rows", "NCNContextFunction",
     "fused_ncn_cuda_ctxlen",
+    "set_stage_backward",
 ]

@@ -8,18 +8,20 @@
 
 namespace ncn {
 
-#ifdef NCN_BWD
-#define NCN_KERNEL feat_bwd_kernel
-#else
-#define NCN_KERNEL feat_fwd_kernel
-#endif
+// NCN_SAVED (with NCN_BWD): the backward that also takes the saved stage input.
 
 template <int LD, int KF, int ACT, typename T>
 static cudaError_t launch_one(const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
   if constexpr (NCN_NC * LD * KF > 1024) {
     return cudaErrorNotSupported;
   } else {
-    auto k = NCN_KERNEL<NCN_NC, LD, KF, ACT, T>;
+#if defined(NCN_BWD) && defined(NCN_SAVED)
+    auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T, true>;
+#elif defined(NCN_BWD)
+    auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T>;
+#else
+    auto k = feat_fwd_kernel<NCN_NC, LD, KF, ACT, T>;
+#endif
     if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, 0);
     k<<<grid, threads, 0, st>>>(p);
     return cudaGetLastError();
@@ -48,7 +50,9 @@ static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid,
 
 #define NCN_CAT2(a, b) a##b
 #define NCN_CAT(a, b) NCN_CAT2(a, b)
-#ifdef NCN_BWD
+#if defined(NCN_BWD) && defined(NCN_SAVED)
+#define NCN_FN NCN_CAT(launch_feat_bwds_n, NCN_NC)
+#elif defined(NCN_BWD)
 #define NCN_FN NCN_CAT(launch_feat_bwd_n, NCN_NC)
 #else
 #define NCN_FN NCN_CAT(launch_feat_fwd_n, NCN_NC)

@@ -698,6 +698,14 @@ static FeatLaunchFn feat_fn(int n, bool bwd) {
   }
 }
 
+static FeatLaunchFn feat_saved_fn(int n) {
+  switch (n) {
+    case 16: return launch_feat_bwds_n16;
+    case 32: return launch_feat_bwds_n32;
+    default: return nullptr;
+  }
+}
+
 static long long gcd_ll(long long a, long long b) {
   while (b) { const long long t = a % b; a = b; b = t; }
   return a;
@@ -707,19 +715,23 @@ static long long gcd_ll(long long a, long long b) {
 // back to the shared-memory kernels); anything else is an error.
 static int launch_feat(bool bwd, const void* const* in, void* const* out, const float* W, float* partials, int64_t B,
                        int64_t N, int64_t E, int n, int C, int module_l, double alpha, int activation, int dtype,
-                       const DevInfo& dev, cudaStream_t st, int* grid_out) {
+                       const DevInfo& dev, cudaStream_t st, int* grid_out, const void* x_saved = nullptr,
+                       const void* xa_saved = nullptr, int saved = 0) {
   const int d = (int)(E / C);
   const int gpw = feat_groups_per_warp(n, d);
-  FeatLaunchFn fn = feat_fn(n, bwd);
+  FeatLaunchFn fn = saved ? feat_saved_fn(n) : feat_fn(n, bwd);
+  if (saved && (!aligned16(x_saved) || !aligned16(xa_saved))) return NCN_ERR_UNSUPPORTED;
   if (gpw == 0 || fn == nullptr || map_act(activation) == ACT_LEAKY) return NCN_ERR_UNSUPPORTED;
   if (env_switches().no_feat) return NCN_ERR_UNSUPPORTED;  // tuning experiments: force the shared-memory kernels
   const int act = fused_act(map_act(activation), dtype);
   for (int q = 0; q < (bwd ? 4 : 2); ++q)
-    if (!aligned16(in[q])) return NCN_ERR_UNSUPPORTED;
+    if (!aligned16(in[q])) return NCN_ERR_UNSUPPORTED;  // (null, where a mode does not read a tensor, counts as aligned)
   for (int q = 0; q < (bwd ? 4 : 2); ++q)
     if (out[q] && !aligned16(out[q])) return NCN_ERR_UNSUPPORTED;
   FeatParams p{};
   for (int q = 0; q < 4; ++q) { p.in[q] = in[q]; p.out[q] = out[q]; }
+  p.xin[0] = x_saved; p.xin[1] = xa_saved;
+  p.saved = saved;
   p.W = W;
   p.partials = partials;
   p.B = B; p.N = (int)N; p.E = (int)E; p.C = C;
@@ -781,9 +793,12 @@ static int stage_fwd_generic(const void* x, const void* xa, const float* W, cons
 static int stage_bwd_generic(const void* y, const void* ya, const void* dy, const void* dya, const float* W,
                              const int* ctxlen, void* dx, void* dxa, void* x_rec, void* xa_rec, float* dW, float* partials,
                              int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha,
-                             int activation, int dtype, const DevInfo& dev, void* stream) {
+                             int activation, int dtype, const DevInfo& dev, void* stream, const void* x_saved = nullptr,
+                             const void* xa_saved = nullptr, int replay_all = 0) {
   StageParams p{};
   fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
+  p.xin[0] = x_saved; p.xin[1] = xa_saved;
+  p.replay_all = replay_all;
   p.in[0] = y; p.in[1] = ya; p.in[2] = dy; p.in[3] = dya;
   p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
   p.W = W;
@@ -816,7 +831,7 @@ using namespace ncn;
 
 extern "C" {
 
-int ncn_version(void) { return 101; }
+int ncn_version(void) { return 102; }
 
 void ncn_reload_env(void) {
   g_env = read_env_switches();
@@ -1089,6 +1104,36 @@ int ncn_stage_bwd(const void* y, const void* ya, const void* dy, const void* dya
   }
   return stage_bwd_generic(y, ya, dy, dya, W, nullptr, dx, dxa, x_rec, xa_rec, dW, static_cast<float*>(workspace), B, N, E,
                            n_cache, n_head, module_l, alpha, activation, dtype, dev, stream);
+}
+
+int ncn_stage_bwd_saved(const void* x, const void* xa, const void* y, const void* ya, const void* dy, const void* dya,
+                        const float* W, void* dx, void* dxa, float* dW, void* workspace, size_t workspace_bytes, int64_t B,
+                        int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                        int dtype, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!x || !xa || !dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  // fp32: the last segment is walked back from the output; bf16: everything is replayed from the input
+  const int replay_all = dtype == DT_BF16 ? 1 : 0;
+  if (!replay_all && (!y || !ya)) return NCN_ERR_NULL;
+  if (!replay_all && n_cache <= kSegment)  // the chain from the output is short enough: the input is not needed
+    return ncn_stage_bwd(y, ya, dy, dya, W, dx, dxa, nullptr, nullptr, dW, workspace, workspace_bytes, B, N, E, n_cache,
+                         n_head, module_l, alpha, activation, dtype, stream);
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  if (!workspace || workspace_bytes < workspace_floats(dev, E, 1) * sizeof(float)) return NCN_ERR_WORKSPACE;
+  {
+    const void* fin[4] = {replay_all ? nullptr : y, replay_all ? nullptr : ya, dy, dya};
+    void* fout[4] = {dx, dxa, nullptr, nullptr};
+    int fgrid = 0;
+    rc = launch_feat(true, fin, fout, W, static_cast<float*>(workspace), B, N, E, n_cache, n_head, module_l, alpha,
+                     activation, dtype, dev, (cudaStream_t)stream, &fgrid, x, xa, replay_all ? 2 : 1);
+    if (rc == NCN_OK) return reduce_dw(static_cast<float*>(workspace), dW, fgrid, 2 * (int)E, 0, (cudaStream_t)stream);
+    if (rc != NCN_ERR_UNSUPPORTED) return rc;
+  }
+  return stage_bwd_generic(y, ya, dy, dya, W, nullptr, dx, dxa, nullptr, nullptr, dW, static_cast<float*>(workspace), B, N,
+                           E, n_cache, n_head, module_l, alpha, activation, dtype, dev, stream, x, xa, replay_all);
 }
 
 int ncn_stage_fwd_ctx(const void* x, const void* xa, const float* W, const int* ctxlen, void* y, void* ya, int64_t B,

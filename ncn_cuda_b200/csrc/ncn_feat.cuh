@@ -35,6 +35,9 @@ namespace ncn {
 struct FeatParams {
   const void* in[4];  // fwd: x, xa ; bwd: y, ya, dy, dya
   void* out[4];       // fwd: y, ya ; bwd: dx, dxa, x_rec|null, xa_rec|null
+  const void* xin[2]; // bwd with the stage input saved: x, xa
+  int saved;          // bwd: 0 = from the output alone; 1 = the first half of the steps is replayed from
+                      // the saved input; 2 = all steps are (y, ya are not read: bf16 storage)
   const float* W;     // [2E]
   float* partials;    // bwd: [gridDim.x][2E]
   long long B;
@@ -218,7 +221,13 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatPar
 // The weight gradient is summed per lane over all its groups, then over the slots of the warp
 // (fixed shuffle tree), the warps of the CTA that serve the same head (warp order) and the CTAs
 // (dw_reduce_kernel): a fixed order for a given launch shape.
-template <int NC, int LD, int KF, int ACT, typename T>
+//
+// SAVED: the caller also kept the stage INPUT.  Every inverse step grows earlier rounding by 1/m, so
+// a chain of NC = 32 steps from the output alone leaves the gradients at 1e-5 of their size; here
+// the state half way is rebuilt exactly by running the forward over the first NC/2 steps from the
+// input, so that no inverse chain is longer than NC/2 steps.  With bf16 storage (p.saved == 2) the
+// end state is replayed too: an inverse started from rounded outputs would amplify their rounding.
+template <int NC, int LD, int KF, int ACT, typename T, bool SAVED = false>
 __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatParams p) {
   using G = FeatGeom<NC, LD, KF>;
   using F = ActForm<ACT>;
@@ -226,6 +235,7 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
   constexpr float sT = (float)F::sT;
   constexpr float cds = (float)(kCd * F::ds);                 // gT = cds * gt
   constexpr float af0 = (float)(-kCd * F::f0 / kMd), af1 = (float)(-kCd * F::f1 / kMd);
+  constexpr float ff0 = (float)(kCd * F::f0), ff1 = (float)(kCd * F::f1);  // forward replay (SAVED)
   __shared__ float sdw[kFeatWarps][2][D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & (LD - 1), slot = lane / LD;
@@ -268,8 +278,10 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
       const int blk = (int)(((long long)g + (long long)i * p.stride) % p.m);
       off[r] = ((b * p.N + (long long)blk * NC + i) * p.E) + fw.c * D + sub * KF;
       if (valid) {
-        ld_feat<KF, T>(g_y + off[r], X[r]);
-        ld_feat<KF, T>(g_ya + off[r], A[r]);
+        if (!(SAVED && p.saved == 2)) {
+          ld_feat<KF, T>(g_y + off[r], X[r]);
+          ld_feat<KF, T>(g_ya + off[r], A[r]);
+        }
         ld_feat<KF, T>(g_dy + off[r], H[r]);
         ld_feat<KF, T>(g_dya + off[r], Gv[r]);
       } else {
@@ -281,6 +293,50 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
     for (int j = NC - 1; j >= 0; --j) {
       // one body for every step: the row index of x_j inside a lane (rj) is a run-time value,
       // resolved by selects, so that the code stays small enough for the instruction cache
+      if constexpr (SAVED) {
+        // the state after step j, exactly: the forward over steps 0..j from the saved input
+        if (j == NC / 2 - 1 || (j == NC - 1 && p.saved == 2)) {
+          const T* g_x = static_cast<const T*>(p.xin[0]);
+          const T* g_xa = static_cast<const T*>(p.xin[1]);
+          if (valid) {
+#pragma unroll
+            for (int r = 0; r < P; ++r) {
+              ld_feat<KF, T>(g_x + off[r], X[r]);
+              ld_feat<KF, T>(g_xa + off[r], A[r]);
+            }
+          }
+#pragma unroll 1
+          for (int jf = 0; jf <= j; ++jf) {
+            const int rf = jf / SEG, sf = jf - rf * SEG;
+            const int srcf = (gw * SEG + sf) * LD + sub;
+            float2 xf[KP];
+            float2 accf = f2(0.0f);
+#pragma unroll
+            for (int q = 0; q < KP; ++q) {
+              float2 v = X[0][q];
+#pragma unroll
+              for (int r = 1; r < P; ++r)
+                if (rf == r) v = X[r][q];
+              xf[q] = shfl2(v, srcf);
+              accf = __ffma2_rn(xf[q], Wj[q], accf);
+            }
+            const float cf = accf.x + accf.y;
+#pragma unroll
+            for (int r = 0; r < P; ++r) {
+              float2 acc = f2(0.0f);
+#pragma unroll
+              for (int q = 0; q < KP; ++q) acc = __ffma2_rn(X[r][q], Wi[q], acc);
+              const float2 sim_s = f2(red_sub<LD>(acc.x + acc.y + cf) * sT);
+#pragma unroll
+              for (int q = 0; q < KP; ++q) {
+                const float2 rr = F::r(__ffma2_rn(sim_s, xf[q], __fmul2_rn(X[r][q], alpha_s)));
+                A[r][q] = __ffma2_rn(rr, f2(ff1), __ffma2_rn(A[r][q], f2(kM), f2(ff0)));
+                X[r][q] = __ffma2_rn(A[r][q], f2(kC), __fmul2_rn(X[r][q], f2(kM)));
+              }
+            }
+          }
+        }
+      }
       const int rj = j / SEG, sj = j - rj * SEG;
       const int src = (gw * SEG + sj) * LD + sub;
       const bool is_j = (s == sj);

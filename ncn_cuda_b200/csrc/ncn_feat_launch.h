@@ -19,6 +19,11 @@ NCN_DECL(8)
 NCN_DECL(16)
 NCN_DECL(32)
 #undef NCN_DECL
+// the backward that also takes the saved stage input (inverse chains of n_cache / 2 steps)
+cudaError_t launch_feat_bwds_n16(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+                                 int* occ);
+cudaError_t launch_feat_bwds_n32(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+                                 int* occ);
 
 // groups a warp works on side by side for (n_cache, d); 0 if there is no kernel
 inline int feat_groups_per_warp(int n, int d) {

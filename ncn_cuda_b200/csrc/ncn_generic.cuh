@@ -18,6 +18,8 @@ struct StageParams {
   const float* W;     // [2E]
   float* partials;    // bwd: [gridDim.x][2E]
   const int* ctxlen;  // [B] context length per batch row, or null: every group takes all n steps
+  const void* xin[2]; // bwd: the saved stage input (x, xa) or null
+  int replay_all;     // bwd with xin: also the last segment starts from replayed values (y, ya are not read)
   long long B;
   long long groups;   // B * C * m
   int N, E, C, d, n, m, stride, ld_shift;  // LD = 1 << ld_shift
@@ -67,6 +69,42 @@ __device__ __forceinline__ long long elem_off(long long b, int pos, int f, int N
   return (b * N + pos) * (long long)E + f;
 }
 
+// One forward step j of a group whose tile sits in shared memory (X, A: [n][pitch]); xj [d] and
+// sim [n] are scratch of the warp.  Used by the forward kernel and by the backward's replay.
+__device__ __forceinline__ void stage_forward_step(const StageParams& p, const int act, float* X, float* A, float* xj,
+                                                   float* sim, const float* Wi, const float* Wj, const int j,
+                                                   const int lane) {
+  const int n = p.n, d = p.d, pitch = p.pitch;
+  const int LD = 1 << p.ld_shift, LT = 32 >> p.ld_shift;
+  const int li = lane >> p.ld_shift, lk = lane & (LD - 1);
+  float cj = 0.0f;
+  for (int k = lane; k < d; k += 32) {
+    const float v = X[j * pitch + k];
+    xj[k] = v;
+    cj = fmaf(v, Wj[k], cj);
+  }
+  cj = warp_sum(cj);
+  __syncwarp();
+  for (int i = lane; i < n; i += 32) {
+    float acc = 0.0f;
+    for (int k = 0; k < d; ++k) acc = fmaf(X[i * pitch + k], Wi[k], acc);
+    sim[i] = (acc + cj) * p.oma;
+  }
+  __syncwarp();
+  for (int i = li; i < n; i += LT) {
+    const float si = sim[i];
+    for (int k = lk; k < d; k += LD) {
+      const float x = X[i * pitch + k];
+      const float t = fmaf(si, xj[k], p.alpha * x);
+      const float f = act_rt(act, t);
+      const float a = fmaf(f, kC, A[i * pitch + k] * kM);
+      A[i * pitch + k] = a;
+      X[i * pitch + k] = fmaf(a, kC, x * kM);
+    }
+  }
+  __syncwarp();
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) stage_fwd_kernel(const StageParams p, const int act) {
   extern __shared__ __align__(16) float sm[];
@@ -100,34 +138,7 @@ __global__ void __launch_bounds__(256) stage_fwd_kernel(const StageParams p, con
     }
     __syncwarp();
     const int steps = group_steps(p.ctxlen, b, g, n);
-    for (int j = 0; j < steps; ++j) {
-      float cj = 0.0f;
-      for (int k = lane; k < d; k += 32) {
-        const float v = X[j * pitch + k];
-        xj[k] = v;
-        cj = fmaf(v, Wj[k], cj);
-      }
-      cj = warp_sum(cj);
-      __syncwarp();
-      for (int i = lane; i < n; i += 32) {
-        float acc = 0.0f;
-        for (int k = 0; k < d; ++k) acc = fmaf(X[i * pitch + k], Wi[k], acc);
-        sim[i] = (acc + cj) * p.oma;
-      }
-      __syncwarp();
-      for (int i = li; i < n; i += LT) {
-        const float si = sim[i];
-        for (int k = lk; k < d; k += LD) {
-          const float x = X[i * pitch + k];
-          const float t = fmaf(si, xj[k], p.alpha * x);
-          const float f = act_rt(act, t);
-          const float a = fmaf(f, kC, A[i * pitch + k] * kM);
-          A[i * pitch + k] = a;
-          X[i * pitch + k] = fmaf(a, kC, x * kM);
-        }
-      }
-      __syncwarp();
-    }
+    for (int j = 0; j < steps; ++j) stage_forward_step(p, act, X, A, xj, sim, Wi, Wj, j, lane);
     for (int i = li; i < n; i += LT) {
       const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
       const long long off = elem_off(b, pos, c * d, p.N, p.E);
@@ -142,6 +153,10 @@ __global__ void __launch_bounds__(256) stage_fwd_kernel(const StageParams p, con
 
 // Backward of one stage from its OUTPUT (reversible reconstruction, as the reference's CUDA
 // backward does); formulas as in group_backward (ncn_common.cuh) with dot products over d.
+// With the stage INPUT saved as well (p.xin), the state at every kSegment-th step is rebuilt by
+// running the forward from the input, so that no inverse chain is longer than kSegment steps
+// (every inverse step grows earlier rounding by 1/m).
+constexpr int kSegment = 16;
 template <typename T>
 __global__ void __launch_bounds__(256) stage_bwd_kernel(const StageParams p, const int act) {
   extern __shared__ __align__(16) float sm[];
@@ -181,14 +196,32 @@ __global__ void __launch_bounds__(256) stage_bwd_kernel(const StageParams p, con
       const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
       const long long off = elem_off(b, pos, c * d, p.N, E);
       for (int k = lk; k < d; k += LD) {
-        X[i * pitch + k] = Store<T>::ld(gy + off + k);
-        A[i * pitch + k] = Store<T>::ld(gya + off + k);
+        if (!p.replay_all) {
+          X[i * pitch + k] = Store<T>::ld(gy + off + k);
+          A[i * pitch + k] = Store<T>::ld(gya + off + k);
+        }
         GX[i * pitch + k] = Store<T>::ld(gdy + off + k);
         GA[i * pitch + k] = Store<T>::ld(gdya + off + k);
       }
     }
     __syncwarp();
-    for (int j = group_steps(p.ctxlen, b, g, n) - 1; j >= 0; --j) {
+    const int steps = group_steps(p.ctxlen, b, g, n);
+    for (int j = steps - 1; j >= 0; --j) {
+      if (p.xin[0] != nullptr && (((j + 1) % kSegment == 0 && j + 1 < steps) || (j == steps - 1 && p.replay_all))) {
+        // the state after step j, exactly: the forward over steps 0..j from the saved input
+        const T* gxi = static_cast<const T*>(p.xin[0]);
+        const T* gxa = static_cast<const T*>(p.xin[1]);
+        for (int i = li; i < n; i += LT) {
+          const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
+          const long long off = elem_off(b, pos, c * d, p.N, E);
+          for (int k = lk; k < d; k += LD) {
+            X[i * pitch + k] = Store<T>::ld(gxi + off + k);
+            A[i * pitch + k] = Store<T>::ld(gxa + off + k);
+          }
+        }
+        __syncwarp();
+        for (int jf = 0; jf <= j; ++jf) stage_forward_step(p, act, X, A, xj, sim, Wi, Wj, jf, lane);
+      }
       // x = (y - c ya) / m
       for (int i = li; i < n; i += LT)
         for (int k = lk; k < d; k += LD) X[i * pitch + k] = fmaf(A[i * pitch + k], -kCoverM, X[i * pitch + k] * kInvM);

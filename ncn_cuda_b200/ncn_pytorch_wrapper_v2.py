@@ -29,14 +29,42 @@ from . import ops
 MAX_INVERSE_STEPS = 16
 
 
+# What the per-stage operator keeps for its backward: "output" = the stage output only, as the
+# reference's NCNFunction does (the input is rebuilt by the reversible inverse over all n_cache
+# steps); "input" = the stage input as well (in a chain of stages it is the previous stage's saved
+# output, so it costs no memory), inverse chains of at most MAX_INVERSE_STEPS steps; "auto" =
+# "input" where the chain from the output would exceed MAX_INVERSE_STEPS steps.
+_STAGE_BACKWARD = "auto"
+
+
+def set_stage_backward(mode: str) -> str:
+    """Chooses what `NCNFunction` saves ("auto" | "output" | "input"); returns the previous choice."""
+    global _STAGE_BACKWARD
+    if mode not in ("auto", "output", "input"):
+        raise ValueError(f"unknown stage backward mode {mode!r}")
+    prev, _STAGE_BACKWARD = _STAGE_BACKWARD, mode
+    return prev
+
+
+def stage_saves_input(n_cache: int) -> bool:
+    if _STAGE_BACKWARD == "auto":
+        return n_cache > MAX_INVERSE_STEPS
+    return _STAGE_BACKWARD == "input"
+
+
 class NCNFunction(torch.autograd.Function):
-    """One stage.  Saves only the stage OUTPUT; backward rebuilds the input by the
-    reversible inverse (ncn_cuda/ncn_pytorch_wrapper_v2.py:9-50)."""
+    """One stage (ncn_cuda/ncn_pytorch_wrapper_v2.py:9-50).  Saves the stage OUTPUT and rebuilds the
+    input by the reversible inverse, as the reference does; for stages of more than
+    MAX_INVERSE_STEPS steps it keeps the stage input too (see set_stage_backward)."""
 
     @staticmethod
     def forward(ctx, x, xa, W, alpha, activation, n_cache, n_head, module_l):
         yi, ya = ops.stage_fwd(x, xa, W, alpha, activation, n_cache, n_head, module_l)
-        ctx.save_for_backward(yi, ya, W)
+        ctx.saves_input = stage_saves_input(n_cache)
+        if ctx.saves_input:
+            ctx.save_for_backward(yi, ya, W, x, xa)
+        else:
+            ctx.save_for_backward(yi, ya, W)
         ctx.alpha = alpha
         ctx.activation = activation
         ctx.n_cache = n_cache
@@ -46,10 +74,16 @@ class NCNFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dyi, dya):
-        (yi, ya, W) = ctx.saved_tensors
-        dx, dxa, dW = ops.stage_bwd(
-            yi, ya, dyi, dya, W, ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l
-        )
+        if ctx.saves_input:
+            (yi, ya, W, x, xa) = ctx.saved_tensors
+            dx, dxa, dW = ops.stage_bwd_saved(
+                x, xa, yi, ya, dyi, dya, W, ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l
+            )
+        else:
+            (yi, ya, W) = ctx.saved_tensors
+            dx, dxa, dW = ops.stage_bwd(
+                yi, ya, dyi, dya, W, ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l
+            )
         return dx, dxa, dW.to(W.dtype), None, None, None, None, None
 
 

@@ -117,6 +117,29 @@ def stage_bwd(y, ya, dy, dya, W, alpha, activation, n_cache, n_head, module_l, w
     return dx, dxa, dW
 
 
+def stage_bwd_saved(x, xa, y, ya, dy, dya, W, alpha, activation, n_cache, n_head, module_l):
+    """Backward of one stage for a caller that kept the stage INPUT too (ncn_stage_bwd_saved): the
+    state at every 16th step is rebuilt by running the forward from (x, xa), so no inverse chain
+    exceeds 16 steps; with bf16 storage everything is replayed from the input.  Returns (dx, dxa, dW[2E])."""
+    lib = _lib.load()
+    _check_inputs(x, xa, y, ya, dy, dya)
+    x, xa, y, ya, dy, dya = (t.contiguous() for t in (x, xa, y, ya, dy, dya))
+    B, N, E = y.shape
+    W = _weights(W, 2 * E, y.device)
+    dx, dxa = torch.empty_like(y), torch.empty_like(y)
+    dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
+    dt = _dtype_code(y)
+    with torch.cuda.device(y.device):
+        ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
+        rc = lib.ncn_stage_bwd_saved(
+            x.data_ptr(), xa.data_ptr(), y.data_ptr(), ya.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(),
+            dx.data_ptr(), dxa.data_ptr(), dW.data_ptr(), ws.data_ptr(), ws.numel(), B, N, E, n_cache, n_head, module_l,
+            float(alpha), activation_code(activation), dt, _stream(),
+        )
+    _lib.check("ncn_stage_bwd_saved", rc)
+    return dx, dxa, dW
+
+
 def _ctxlen(ctxlen, B, device) -> torch.Tensor:
     ctxlen = torch.as_tensor(ctxlen)
     if ctxlen.numel() != B:
