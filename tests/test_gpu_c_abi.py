@@ -52,7 +52,9 @@ def test_c_host_matches_oracle(host_binary, tmp_path, B, N, n, L, every, act, co
     y, ya, dx, dxa = (torch.from_numpy(out[k * bn:(k + 1) * bn].copy()).reshape(B, N, 1) for k in range(4))
     dW = torch.from_numpy(out[4 * bn:].copy()).reshape(L, 2)
     ry, rya, rdx, rdxa, rdW = O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, act, n, 1)
-    tol = 1e-5 if (every or n * L <= 16) else 5e-5
+    tol = 1e-5  # also for the 24 rebuilt steps of the third case (measured 1.3e-6)
+    print("\nerrors against bound %g:" % tol, ["%.2e" % O.rel_err(a, b) for a, b in
+          ((y, ry), (ya, rya), (dx, rdx), (dxa, rdxa), (dW, torch.stack(list(rdW))))])  # shown with pytest -s
     assert O.rel_err(y, ry) < 1e-5 and O.rel_err(ya, rya) < 1e-5
     assert O.rel_err(dx, rdx) < tol and O.rel_err(dxa, rdxa) < tol
     assert O.rel_err(dW, torch.stack(list(rdW))) < tol

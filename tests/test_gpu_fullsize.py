@@ -49,9 +49,9 @@ def test_fp32_full_size(ncn, name, B, N, n, L, var, seed, every):
     y, ya, dx, dxa, dW, xr, xar = _run(ncn, x, xa, dy, dya, W, n, every, want_inputs=True)
     ncn.ops.device_status()
     # round trip through forward + reversible backward.  Each rebuilt step grows earlier rounding by
-    # 1/0.9: chains of <= 16 steps (checkpointed) stay near 1e-5 in the worst of 2.7e8 elements, the
-    # 32-step chain of the checkpoint-free variant reaches ~1e-4.
-    rt_tol = 2e-5 if every else 2e-4
+    # 1/0.9: chains of <= 16 steps (checkpointed) stay at 1e-6 in the worst of 2.7e8 elements (measured 8.6e-7),
+    # the 32-step chain of the checkpoint-free variant reaches 1.3e-5 (xa: 7e-5 absolute).
+    rt_tol = 1e-5 if every else 5e-5
     assert O.rel_err(xr, x) < rt_tol, O.rel_err(xr, x)
     assert float((xar - xa).abs().max()) < rt_tol * 4
     # a slice of rows taken from the middle of the batch, run alone
@@ -63,10 +63,12 @@ def test_fp32_full_size(ncn, name, B, N, n, L, var, seed, every):
     ws = [W[l].cpu() for l in range(L)]
     ry, rya, rdx, rdxa, rdW = O.net_fwd_bwd(x[lo:hi].cpu(), xa[lo:hi].cpu(), ws, dy[lo:hi].cpu(), dya[lo:hi].cpu(), 0.9, "tanh", n, 1)
     tol = 1e-5
+    print("\nround trip", O.rel_err(xr, x), float((xar - xa).abs().max()), "errors", ["%.2e" % O.rel_err(a, b) for a, b in
+          ((sy, ry), (sya, rya), (sdx, rdx), (sdxa, rdxa))], ["%.2e" % O.rel_err(sdW[l], rdW[l]) for l in range(L)])
     assert O.rel_err(sy, ry) < tol and O.rel_err(sya, rya) < tol
     assert O.rel_err(sdx, rdx) < tol and O.rel_err(sdxa, rdxa) < tol
     for l in range(L):
-        assert O.rel_err(sdW[l], rdW[l]) < 2e-5, (l, O.rel_err(sdW[l], rdW[l]))
+        assert O.rel_err(sdW[l], rdW[l]) < 1e-5, (l, O.rel_err(sdW[l], rdW[l]))  # measured up to 5.5e-6 (config 4, from the output)
     # dW is additive over parts of the batch
     acc = torch.zeros_like(dW)
     q = B // 4

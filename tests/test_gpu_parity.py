@@ -45,6 +45,8 @@ def run_net(ncn, cls_name, g_or_inputs, activation, n, C, backward_mode=None, dt
 def assert_close(got, want, tol):
     y, ya, dx, dxa, dWs = got
     ry, rya, rdx, rdxa, rdWs = want
+    print("\nerrors (y, ya, dx, dxa, dW...) against bound %g:" % tol, ["%.2e" % O.rel_err(a.float(), b) for a, b in
+          list(zip((y, ya, dx, dxa), (ry, rya, rdx, rdxa))) + list(zip(dWs, rdWs))])  # shown with pytest -s
     assert O.rel_err(y.float(), ry) < tol, ("y", O.rel_err(y.float(), ry))
     assert O.rel_err(ya.float(), rya) < tol, ("ya", O.rel_err(ya.float(), rya))
     assert O.rel_err(dx.float(), rdx) < tol, ("dx", O.rel_err(dx.float(), rdx))
@@ -71,8 +73,8 @@ def test_golden_invertible_surface(ncn, name):
     inputs = (g["x"], g["xa"], g["W"], g["dy"], g["dya"])
     got = run_net(ncn, "RefInvTorchNaive", inputs, g["activation"], g["n"], g["C"])
     want = (g["y"], g["ya"], g["dx"], g["dxa"], g["dW"])
-    # 24-32 inverse steps: a few 1e-6 on dx, up to ~1e-5 on a two-element dW of one row
-    assert_close(got, want, 3e-5)
+    # 24-32 inverse steps from the output alone: measured up to 7.2e-6 (dx of the config-4 case)
+    assert_close(got, want, 2e-5)
 
 
 def test_golden_reftorchnaive_surface(ncn):
@@ -323,10 +325,11 @@ def test_net_modes(ncn, B, N, n, L, var, act, mode):
     want = O.net_fwd_bwd(x, xa, ws, dy, dya, 0.9, act, n, 1)
     got = run_net(ncn, "NCNNetTestCuda", inputs, act, n, 1, backward_mode=mode)
     steps = n * L
-    if mode == "invert":  # rounding grows 1/0.9 per rebuilt step
-        tol = TOL32 if steps <= 16 else (5e-5 if steps <= 40 else 1e-2)
-    elif mode == "recompute":
-        tol = TOL32 if steps <= 16 else (5e-5 if steps <= 40 else 1e-2)
+    if mode in ("invert", "recompute") and 16 < steps <= 40:
+        # every step is rebuilt from the net output (or from the replayed output): rounding grows 1/0.9 per step,
+        # measured up to 1.1e-5 (a dW element of the 28-step linear case).  The one case beyond 40 steps
+        # (8192 x 16 x 4 stages in fp32) does not fit the fused backward and runs stage by stage: 16-step chains.
+        tol = 2e-5
     else:
         tol = TOL32
     assert_close(got, want, tol)
