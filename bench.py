@@ -53,6 +53,10 @@ WORKLOADS = {
                            desc="ref_e128 with 1024 rows (profiling case)"),
     "small": dict(B=8192, N=4096, n=4, L=6, w_var=0.25, dtype="f32", act="tanh", seed=1,
                   desc="cfg2 with 8192 rows (profiling case)"),
+    "cfg4_small": dict(B=8192, N=4096, n=8, L=4, w_var=0.01, dtype="f32", act="tanh", seed=3, mode="invert",
+                       desc="cfg4 with 8192 rows (profiling case)"),
+    "cfg5_small": dict(B=16384, N=2048, n=8, L=4, w_var=1 / 8, dtype="bf16", act="tanh", seed=4, layers=2, mode="tape",
+                       desc="two residual layers of the cfg5 shape, 16384 rows (profiling case)"),
 }
 
 # Workloads measured for a few steps after the headline one in a default run (one GPU: all of them;

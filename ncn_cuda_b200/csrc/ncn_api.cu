@@ -59,7 +59,7 @@ static int get_dev(DevInfo& out) {
 // measurements; the defaults are the fastest measured).
 struct EnvSwitches {
   bool exact_tanh, no_pair, no_feat, bwd_wide_off, bwd_dual_off, fwd_dual_off, lanes_off, lanes_pipe_off;
-  int fwd_threads, bwd_threads, nbuf;
+  int fwd_threads, bwd_threads, nbuf, lane_rows;
 };
 static EnvSwitches read_env_switches() {
   auto is = [](const char* name, char c) {
@@ -82,6 +82,7 @@ static EnvSwitches read_env_switches() {
   v.fwd_threads = num("NCN_FWD_THREADS");
   v.bwd_threads = num("NCN_BWD_THREADS");
   v.nbuf = num("NCN_NBUF");
+  v.lane_rows = num("NCN_LANE_ROWS");
   return v;
 }
 static EnvSwitches g_env = read_env_switches();
@@ -543,9 +544,19 @@ static int plan_lanes(bool bwd, int64_t B, int64_t N, int64_t E, int n, int C, i
   const int G = lane_groups(n);
   const int tpr = (int)(N / n) / G;
   int R = kLaneThreads / tpr;
+  {
+    // A CTA is one barrier domain.  With plenty of tiles per CTA, halves of kLaneThreads do better (more,
+    // smaller domains per SM drift apart and fill each other's waits: the 12-layer bf16 stack 89.7 -> 84.3 ms);
+    // with about one tile per CTA the per-CTA set-up counts and the larger tile wins (1024 x 1024: 0.23 against
+    // 0.28 ms backward).
+    const int r_small = kLaneThreads / 2 / tpr;
+    if (r_small >= 1 && B / r_small >= 8LL * dev.sms * (bwd ? kLaneBwdBlocks : kLaneFwdBlocks) * 2) R = r_small;
+  }
+  if (env_switches().lane_rows > 0 && R > env_switches().lane_rows) R = env_switches().lane_rows;
   if ((int64_t)R > B) R = (int)B;
   if (R < 1) R = 1;
-  const int want_occ = bwd ? kLaneBwdBlocks : kLaneFwdBlocks;
+  // the register budget allows kLane*Blocks CTAs of kLaneThreads threads: smaller CTAs, more of them
+  const int want_occ = (bwd ? kLaneBwdBlocks : kLaneFwdBlocks) * (kLaneThreads / (R * tpr));
   const int cap = lane_ea_cap(n);
   int ea_hi = e_need < cap ? e_need : cap;
   int ea_lo = lane_ilog2(G) - 1;  // longer shifts through the tile buffer must be multiples of G blocks
