@@ -60,6 +60,7 @@ static int get_dev(DevInfo& out) {
 struct EnvSwitches {
   bool exact_tanh, no_pair, no_feat, bwd_wide_off, bwd_dual_off, fwd_dual_off, lanes_off, lanes_pipe_off;
   int fwd_threads, bwd_threads, nbuf, lane_rows;
+  bool test_short_wait;  // NCN_TEST_SHORT_WAIT=1: the lane forward gives up its first wait (tests of that path)
 };
 static EnvSwitches read_env_switches() {
   auto is = [](const char* name, char c) {
@@ -83,6 +84,7 @@ static EnvSwitches read_env_switches() {
   v.bwd_threads = num("NCN_BWD_THREADS");
   v.nbuf = num("NCN_NBUF");
   v.lane_rows = num("NCN_LANE_ROWS");
+  v.test_short_wait = is("NCN_TEST_SHORT_WAIT", '1');
   return v;
 }
 static EnvSwitches g_env = read_env_switches();
@@ -954,6 +956,7 @@ int ncn_net_fwd(const void* x, const void* xa, const float* W, void* y, void* ya
       q.alpha = (float)alpha;
       q.oma = (float)(1.0 - alpha);
       fill_lane(q, lp);
+      q.test_short_wait = env_switches().test_short_wait ? 1 : 0;
       cudaError_t e = lane_fn(n_cache, false)(act, dtype, q, lp.grid, lp.threads, lp.smem, (cudaStream_t)stream, nullptr);
       return e == cudaSuccess ? NCN_OK : cuda_fail(e);
     }

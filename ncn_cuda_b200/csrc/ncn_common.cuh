@@ -63,8 +63,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: gives up after ~2^22 polls (each poll may itself suspend for a
 // hardware-defined time), so a copy that never lands cannot hang the GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t tries = 1u << 22) {
+  for (uint32_t it = 0; it < tries; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   return false;

@@ -499,7 +499,9 @@ __global__ void __launch_bounds__(MAXT, MINB) lane_fwd_kernel(const LaneParams p
     const long long row0 = tl * R;
     const int rows = (int)min((long long)R, p.B - row0);
     const uint32_t bytes = (uint32_t)(rows * N * sizeof(T));
-    mbar_expect_tx(&bar[0], (residual ? 3 : 2) * bytes);
+    // (test_short_wait, set by tests of the give-up path only: the barrier expects 16 bytes more than are sent,
+    //  so its phase never completes; every copy that IS issued completes as usual)
+    mbar_expect_tx(&bar[0], (residual ? 3 : 2) * bytes + (p.test_short_wait ? 16u : 0u));
     bulk_g2s(win, gx_in + row0 * N, bytes, &bar[0]);
     bulk_g2s(win + RN, ga_in + row0 * N, bytes, &bar[0]);
     if (residual) bulk_g2s(sres, gx_in + row0 * N, bytes, &bar[0]);
@@ -527,7 +529,7 @@ __global__ void __launch_bounds__(MAXT, MINB) lane_fwd_kernel(const LaneParams p
       bulk_wait_read0();  // the previous tile's stores have left the buffer
       issue_load(tile);
     }
-    if (!mbar_wait_bounded(&bar[0], phase)) *abort_flag = 1;
+    if (!mbar_wait_bounded(&bar[0], phase, p.test_short_wait ? (1u << 10) : (1u << 22))) *abort_flag = 1;
     phase ^= 1;
     __syncthreads();
     if (*abort_flag) break;

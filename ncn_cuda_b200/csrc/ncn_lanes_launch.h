@@ -20,6 +20,7 @@ struct LaneParams {
   uint32_t off_work, off_res, off_ckpt, off_halo, off_red, off_w, off_bar;
   uint32_t halo_warp_bytes;  // halo bytes per warp and buffer
   uint32_t n_ckpt_slots;
+  int test_short_wait;       // forward, tests of the give-up path only: expect 16 bytes that never come, poll 2^10 times
   int pipelined;             // backward, n = 4: the kernel of ncn_lanes_pipe.cuh (halo inside the tile buffer)
 };
 

@@ -494,6 +494,37 @@ def test_error_behaviour(ncn):
     ncn.ops.device_status()
 
 
+def test_abandoned_wait_is_reported_and_the_library_stays_usable(ncn, monkeypatch):
+    """The give-up path of a bounded wait, without a fault and without a hang: with NCN_TEST_SHORT_WAIT=1 the
+    forward's barrier expects 16 bytes more than the (complete, correct) copies deliver and polls 2^10 times
+    instead of 2^22, so the wait runs out.  Every CTA then leaves its tile loop, the status word is set once,
+    ncn_device_status() reports and clears it, and the next ordinary call is exact again."""
+    from ncn_cuda_b200 import _lib
+    from ncn_cuda_b200._lib import NCNError
+
+    lib = _lib.load()
+    B, N, n, L = 8, 512, 4, 3
+    x, xa, ws, dy, dya = O.make_inputs(11, B, N, 1, L, 0.25, dya_zero=False)
+    W = dev(torch.stack(ws))
+    xd, xad = dev(x), dev(xa)
+    ncn.ops.device_status()
+    monkeypatch.setenv("NCN_TEST_SHORT_WAIT", "1")
+    lib.ncn_reload_env()
+    try:
+        ncn.ops.net_fwd(xd, xad, W, 0.9, 0, n, 1)      # launches; its kernel gives the wait up
+        with pytest.raises(NCNError) as e:
+            ncn.ops.device_status()
+        assert e.value.status == 9                      # NCN_ERR_DEVICE_WAIT
+        ncn.ops.device_status()                         # reading it cleared it
+    finally:
+        monkeypatch.delenv("NCN_TEST_SHORT_WAIT")
+        lib.ncn_reload_env()
+    y, ya, _ = ncn.ops.net_fwd(xd, xad, W, 0.9, 0, n, 1)
+    ncn.ops.device_status()
+    ry, rya = O.net_forward(x, xa, ws, 0.9, "tanh", n, 1)
+    assert O.rel_err(y, ry) < TOL32 and O.rel_err(ya, rya) < TOL32
+
+
 # ---------------------------------------------------------------- host-buffer entry (the e2e path of bench.py)
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL32), (torch.bfloat16, TOLBF)])
 def test_host_buffer_pipeline(ncn, dtype, tol):
