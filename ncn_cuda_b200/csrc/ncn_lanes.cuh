@@ -576,9 +576,16 @@ __global__ void __launch_bounds__(MAXT, MINB) lane_fwd_kernel(const LaneParams p
 #pragma unroll
         for (int s = 0; s < 2; ++s)
 #pragma unroll
-          for (int o = 0; o < NG; ++o)
+          for (int o = 0; o < NG; ++o) {
+            if constexpr (G >= 4) {  // a thread's pairs are neighbours in memory: whole 16-byte stores
 #pragma unroll
-            for (int pp = 0; pp < G / 2; ++pp) ck[(s * NG + o) * (m >> 1) + pp] = V[s][pp][o];
+              for (int pp = 0; pp < G / 2; pp += 2)
+                *reinterpret_cast<float4*>(ck + (s * NG + o) * (m >> 1) + pp) =
+                    make_float4(V[s][pp][o].x, V[s][pp][o].y, V[s][pp + 1][o].x, V[s][pp + 1][o].y);
+            } else {
+              ck[(s * NG + o) * (m >> 1)] = V[s][0][o];
+            }
+          }
       }
     }
     lane_exchange<NG, G, 2>(V, -s_cur, p.ea_max, halo, lane, xrow, t, m);  // back to stride 0 = native order
