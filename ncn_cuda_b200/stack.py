@@ -74,8 +74,10 @@ def allreduce_weight_grads(params: Iterable[torch.Tensor], group=None, determini
         flat = total
     else:
         dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-    off = 0
+    # one multi-tensor copy back (a launch per stage would sit, serial, behind every backward)
+    views, off = [], 0
     for g in grads:
         n = g.numel()
-        g.copy_(flat[off : off + n].reshape(g.shape))
+        views.append(flat[off : off + n].reshape(g.shape))
         off += n
+    torch._foreach_copy_(grads, views)
