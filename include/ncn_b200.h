@@ -173,7 +173,7 @@ const char* ncn_last_cuda_error(void);
 /* Library version (major*100 + minor). */
 int ncn_version(void);
 
-/* The NCN_* environment switches (kernel selection for A/B measurements) are read once,
+/* The NCN_* environment switches (kernel selection for A/B measurements: NCN_LANES, NCN_LANES_PIPE, NCN_FWD_DUAL, NCN_BWD_DUAL, NCN_NO_PAIR, NCN_NO_FEAT, NCN_EXACT_TANH, ...) are read once,
  * when the library is loaded, and launch plans are remembered per argument set.  This call reads the
  * switches again and forgets the remembered plans.  Not thread-safe against concurrent launches.
  * No counterpart in the reference (which has no such switches). */
