@@ -46,6 +46,10 @@ WORKLOADS = {
     "ref_e128": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5, stage_keep="output",
                      desc="the reference's own bench shape scaled in rows: x[4096,256,128] 4 heads g=32 3 stages, one kernel per "
                           "stage, backward from each stage's output alone (the reference operator's contract)"),
+    "ref_e128_mid": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
+                         stage_keep="mid",
+                         desc="ref_e128 with the state after step 16 of every stage stored by the forward (inverse chains of 16 "
+                              "steps: 1e-5 gradients; what the operator does by default)"),
     "ref_e128_input": dict(B=4096, N=256, E=128, C=4, n=32, L=3, w_var=1 / 32, dtype="f32", act="tanh", seed=5,
                            stage_keep="input",
                            desc="ref_e128 with the stage inputs kept for the backward (inverse chains of 16 steps: 1e-5 gradients)"),

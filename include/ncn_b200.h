@@ -90,6 +90,22 @@ int ncn_stage_bwd_saved(const void* x, const void* xa, const void* y, const void
                         int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
                         int dtype, void* stream);
 
+/* The same accuracy without the replay, for callers that can spend memory instead: the forward also stores the
+ * fp32 state after every 16th step short of the last (n_cache = 32: one state, 8 bytes per element; with bf16
+ * storage the state after the last step too, and the backward then reads neither y nor ya, which may be null),
+ * and the backward restarts its inverse there.  No counterpart in the reference.  `mid` is opaque to the caller:
+ * ncn_stage_mid_bytes(...) bytes of device memory, 16-byte aligned, written by ncn_stage_fwd_mid and handed
+ * unchanged to ncn_stage_bwd_mid with the same shape arguments.  Where ncn_stage_mid_bytes is 0 (fp32 storage,
+ * n_cache <= 16) the calls are ncn_stage_fwd / ncn_stage_bwd and mid may be null. */
+size_t ncn_stage_mid_bytes(int64_t B, int64_t N, int64_t E, int n_cache, int dtype);
+int ncn_stage_fwd_mid(const void* x, const void* xa, const float* W, void* y, void* ya, void* mid, size_t mid_bytes,
+                      int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                      int dtype, void* stream);
+int ncn_stage_bwd_mid(const void* y, const void* ya, const void* mid, size_t mid_bytes, const void* dy, const void* dya,
+                      const float* W, void* dx, void* dxa, float* dW, void* workspace, size_t workspace_bytes, int64_t B,
+                      int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                      int dtype, void* stream);
+
 /* One stage with a context length per batch row, forward and backward.  Replace the step-count rule of the
  * reference's earlier Triton operator (ncn_triton/ncn_triton_old.py:70-96 forward, :186-197 backward:
  * `ctxlen = load(ctxlen_tensor + batch)`, `hi = GROUP if group*GROUP + GROUP < ctxlen else ctxlen - group*GROUP`,

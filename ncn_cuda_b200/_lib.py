@@ -27,6 +27,16 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 10 + [c_void_p, c_size_t] + [c_int64] * 3 + [c_int] * 3 + [c_double, c_int, c_int, c_void_p],
     ),
+    "ncn_stage_mid_bytes": (c_size_t, [c_int64] * 3 + [c_int, c_int]),
+    "ncn_stage_fwd_mid": (
+        c_int,
+        [c_void_p] * 5 + [c_void_p, c_size_t] + [c_int64] * 3 + [c_int] * 3 + [c_double, c_int, c_int, c_void_p],
+    ),
+    "ncn_stage_bwd_mid": (
+        c_int,
+        [c_void_p] * 2 + [c_void_p, c_size_t] + [c_void_p] * 6 + [c_void_p, c_size_t] + [c_int64] * 3 + [c_int] * 3
+        + [c_double, c_int, c_int, c_void_p],
+    ),
     "ncn_stage_fwd_ctx": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 3 + [c_double, c_int, c_int, c_void_p]),
     "ncn_stage_bwd_ctx": (
         c_int,

@@ -8,7 +8,8 @@
 
 namespace ncn {
 
-// NCN_SAVED (with NCN_BWD): the backward that also takes the saved stage input.
+// NCN_SAVED (with NCN_BWD): the backward that also takes the saved stage input or the forward's stored states.
+// NCN_MID (without NCN_BWD): the forward that stores the state after every 16th step.
 
 template <int LD, int KF, int ACT, typename T>
 static cudaError_t launch_one(const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
@@ -19,6 +20,8 @@ static cudaError_t launch_one(const FeatParams& p, int grid, int threads, cudaSt
     auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T, true>;
 #elif defined(NCN_BWD)
     auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T>;
+#elif defined(NCN_MID)
+    auto k = feat_fwd_kernel<NCN_NC, LD, KF, ACT, T, true>;
 #else
     auto k = feat_fwd_kernel<NCN_NC, LD, KF, ACT, T>;
 #endif
@@ -54,6 +57,8 @@ static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid,
 #define NCN_FN NCN_CAT(launch_feat_bwds_n, NCN_NC)
 #elif defined(NCN_BWD)
 #define NCN_FN NCN_CAT(launch_feat_bwd_n, NCN_NC)
+#elif defined(NCN_MID)
+#define NCN_FN NCN_CAT(launch_feat_fwdm_n, NCN_NC)
 #else
 #define NCN_FN NCN_CAT(launch_feat_fwd_n, NCN_NC)
 #endif

@@ -711,6 +711,14 @@ static FeatLaunchFn feat_fn(int n, bool bwd) {
   }
 }
 
+static FeatLaunchFn feat_mid_fn(int n) {
+  switch (n) {
+    case 16: return launch_feat_fwdm_n16;
+    case 32: return launch_feat_fwdm_n32;
+    default: return nullptr;
+  }
+}
+
 static FeatLaunchFn feat_saved_fn(int n) {
   switch (n) {
     case 16: return launch_feat_bwds_n16;
@@ -729,11 +737,12 @@ static long long gcd_ll(long long a, long long b) {
 static int launch_feat(bool bwd, const void* const* in, void* const* out, const float* W, float* partials, int64_t B,
                        int64_t N, int64_t E, int n, int C, int module_l, double alpha, int activation, int dtype,
                        const DevInfo& dev, cudaStream_t st, int* grid_out, const void* x_saved = nullptr,
-                       const void* xa_saved = nullptr, int saved = 0) {
+                       const void* xa_saved = nullptr, int saved = 0, float* mid = nullptr, int mid_end = 0) {
   const int d = (int)(E / C);
   const int gpw = feat_groups_per_warp(n, d);
-  FeatLaunchFn fn = saved ? feat_saved_fn(n) : feat_fn(n, bwd);
-  if (saved && (!aligned16(x_saved) || !aligned16(xa_saved))) return NCN_ERR_UNSUPPORTED;
+  FeatLaunchFn fn = saved ? feat_saved_fn(n) : (mid && !bwd) ? feat_mid_fn(n) : feat_fn(n, bwd);
+  if (saved && saved != 3 && (!aligned16(x_saved) || !aligned16(xa_saved))) return NCN_ERR_UNSUPPORTED;
+  if (mid && !aligned16(mid)) return NCN_ERR_UNSUPPORTED;
   if (gpw == 0 || fn == nullptr || map_act(activation) == ACT_LEAKY) return NCN_ERR_UNSUPPORTED;
   if (env_switches().no_feat) return NCN_ERR_UNSUPPORTED;  // tuning experiments: force the shared-memory kernels
   const int act = fused_act(map_act(activation), dtype);
@@ -745,6 +754,7 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
   for (int q = 0; q < 4; ++q) { p.in[q] = in[q]; p.out[q] = out[q]; }
   p.xin[0] = x_saved; p.xin[1] = xa_saved;
   p.saved = saved;
+  p.mid = mid; p.mid_end = mid_end; p.bne = B * N * E;
   p.W = W;
   p.partials = partials;
   p.B = B; p.N = (int)N; p.E = (int)E; p.C = C;
@@ -780,13 +790,14 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
 // ---- per-stage launches of the shared-memory kernels (any E, heads, n_cache; optional per-row context length)
 static int stage_fwd_generic(const void* x, const void* xa, const float* W, const int* ctxlen, void* y, void* ya, int64_t B,
                              int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
-                             int dtype, const DevInfo& dev, void* stream) {
+                             int dtype, const DevInfo& dev, void* stream, float* mid = nullptr, int mid_end = 0) {
   StageParams p{};
   fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
   p.in[0] = x; p.in[1] = xa;
   p.out[0] = y; p.out[1] = ya;
   p.W = W;
   p.ctxlen = ctxlen;
+  p.mid = mid; p.mid_end = mid_end; p.bne = B * N * E;
   GenericPlan g;
   int rc;
   const int act = map_act(activation);
@@ -807,11 +818,13 @@ static int stage_bwd_generic(const void* y, const void* ya, const void* dy, cons
                              const int* ctxlen, void* dx, void* dxa, void* x_rec, void* xa_rec, float* dW, float* partials,
                              int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha,
                              int activation, int dtype, const DevInfo& dev, void* stream, const void* x_saved = nullptr,
-                             const void* xa_saved = nullptr, int replay_all = 0) {
+                             const void* xa_saved = nullptr, int replay_all = 0, const float* mid = nullptr,
+                             int mid_end = 0) {
   StageParams p{};
   fill_stage(p, B, N, E, n_cache, n_head, module_l, alpha);
   p.xin[0] = x_saved; p.xin[1] = xa_saved;
   p.replay_all = replay_all;
+  p.mid = const_cast<float*>(mid); p.mid_end = mid_end; p.bne = B * N * E;
   p.in[0] = y; p.in[1] = ya; p.in[2] = dy; p.in[3] = dya;
   p.out[0] = dx; p.out[1] = dxa; p.out[2] = x_rec; p.out[3] = xa_rec;
   p.W = W;
@@ -844,7 +857,7 @@ using namespace ncn;
 
 extern "C" {
 
-int ncn_version(void) { return 102; }
+int ncn_version(void) { return 103; }
 
 void ncn_reload_env(void) {
   g_env = read_env_switches();
@@ -1148,6 +1161,75 @@ int ncn_stage_bwd_saved(const void* x, const void* xa, const void* y, const void
   }
   return stage_bwd_generic(y, ya, dy, dya, W, nullptr, dx, dxa, nullptr, nullptr, dW, static_cast<float*>(workspace), B, N,
                            E, n_cache, n_head, module_l, alpha, activation, dtype, dev, stream, x, xa, replay_all);
+}
+
+// states the per-stage forward stores for ncn_stage_bwd_mid: one after every 16th step short of the last, and with
+// bf16 storage the end state too
+static int stage_mid_states(int n_cache, int dtype) { return (n_cache - 1) / kSegment + (dtype == DT_BF16 ? 1 : 0); }
+
+size_t ncn_stage_mid_bytes(int64_t B, int64_t N, int64_t E, int n_cache, int dtype) {
+  if (B <= 0 || N <= 0 || E <= 0 || n_cache <= 0) return 0;
+  return (size_t)stage_mid_states(n_cache, dtype) * 2 * (size_t)B * (size_t)N * (size_t)E * sizeof(float);
+}
+
+int ncn_stage_fwd_mid(const void* x, const void* xa, const float* W, void* y, void* ya, void* mid, size_t mid_bytes,
+                      int64_t B, int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                      int dtype, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!x || !xa || !W || !y || !ya) return NCN_ERR_NULL;
+  const size_t need = ncn_stage_mid_bytes(B, N, E, n_cache, dtype);
+  if (need == 0)  // nothing to store: chains of at most 16 steps from fp32 outputs
+    return ncn_stage_fwd(x, xa, W, y, ya, B, N, E, n_cache, n_head, module_l, alpha, activation, dtype, stream);
+  if (!mid) return NCN_ERR_NULL;
+  if (mid_bytes < need) return NCN_ERR_WORKSPACE;
+  const int mid_end = dtype == DT_BF16 ? 1 : 0;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  {
+    const void* fin[4] = {x, xa, nullptr, nullptr};
+    void* fout[4] = {y, ya, nullptr, nullptr};
+    rc = launch_feat(false, fin, fout, W, nullptr, B, N, E, n_cache, n_head, module_l, alpha, activation, dtype, dev,
+                     (cudaStream_t)stream, nullptr, nullptr, nullptr, 0, static_cast<float*>(mid), mid_end);
+    if (rc != NCN_ERR_UNSUPPORTED) return rc;
+  }
+  return stage_fwd_generic(x, xa, W, nullptr, y, ya, B, N, E, n_cache, n_head, module_l, alpha, activation, dtype, dev,
+                           stream, static_cast<float*>(mid), mid_end);
+}
+
+int ncn_stage_bwd_mid(const void* y, const void* ya, const void* mid, size_t mid_bytes, const void* dy, const void* dya,
+                      const float* W, void* dx, void* dxa, float* dW, void* workspace, size_t workspace_bytes, int64_t B,
+                      int64_t N, int64_t E, int n_cache, int n_head, int module_l, double alpha, int activation,
+                      int dtype, void* stream) {
+  int rc = check_common(B, N, E, n_cache, n_head, dtype);
+  if (rc != NCN_OK) return rc;
+  if (module_l < 0) return NCN_ERR_SHAPE;
+  if (!dy || !dya || !W || !dx || !dxa || !dW) return NCN_ERR_NULL;
+  const size_t need = ncn_stage_mid_bytes(B, N, E, n_cache, dtype);
+  if (need == 0)
+    return ncn_stage_bwd(y, ya, dy, dya, W, dx, dxa, nullptr, nullptr, dW, workspace, workspace_bytes, B, N, E, n_cache,
+                         n_head, module_l, alpha, activation, dtype, stream);
+  if (!mid) return NCN_ERR_NULL;
+  if (mid_bytes < need) return NCN_ERR_WORKSPACE;
+  const int mid_end = dtype == DT_BF16 ? 1 : 0;
+  if (!mid_end && (!y || !ya)) return NCN_ERR_NULL;
+  DevInfo dev;
+  if ((rc = get_dev(dev)) != NCN_OK) return rc;
+  if (!workspace || workspace_bytes < workspace_floats(dev, E, 1) * sizeof(float)) return NCN_ERR_WORKSPACE;
+  {
+    const void* fin[4] = {mid_end ? nullptr : y, mid_end ? nullptr : ya, dy, dya};
+    void* fout[4] = {dx, dxa, nullptr, nullptr};
+    int fgrid = 0;
+    rc = launch_feat(true, fin, fout, W, static_cast<float*>(workspace), B, N, E, n_cache, n_head, module_l, alpha,
+                     activation, dtype, dev, (cudaStream_t)stream, &fgrid, nullptr, nullptr, 3,
+                     const_cast<float*>(static_cast<const float*>(mid)), mid_end);
+    if (rc == NCN_OK) return reduce_dw(static_cast<float*>(workspace), dW, fgrid, 2 * (int)E, 0, (cudaStream_t)stream);
+    if (rc != NCN_ERR_UNSUPPORTED) return rc;
+  }
+  return stage_bwd_generic(y, ya, dy, dya, W, nullptr, dx, dxa, nullptr, nullptr, dW, static_cast<float*>(workspace), B, N,
+                           E, n_cache, n_head, module_l, alpha, activation, dtype, dev, stream, nullptr, nullptr, 0,
+                           static_cast<const float*>(mid), mid_end);
 }
 
 int ncn_stage_fwd_ctx(const void* x, const void* xa, const float* W, const int* ctxlen, void* y, void* ya, int64_t B,

@@ -37,7 +37,12 @@ struct FeatParams {
   void* out[4];       // fwd: y, ya ; bwd: dx, dxa, x_rec|null, xa_rec|null
   const void* xin[2]; // bwd with the stage input saved: x, xa
   int saved;          // bwd: 0 = from the output alone; 1 = the first half of the steps is replayed from
-                      // the saved input; 2 = all steps are (y, ya are not read: bf16 storage)
+                      // the saved input; 2 = all steps are (y, ya are not read: bf16 storage); 3 = the states
+                      // the forward stored in `mid` replace the rebuilt ones
+  float* mid;         // fp32 states after every 16th step: state k, stream s at mid + (2k + s) * bne, in the
+                      // element order of the activations (fwd with MID: written; bwd with saved == 3: read)
+  long long bne;      // elements per activation tensor
+  int mid_end;        // the state after the LAST step is stored / read as well (bf16 storage: y, ya are not read)
   const float* W;     // [2E]
   float* partials;    // bwd: [gridDim.x][2E]
   long long B;
@@ -111,7 +116,9 @@ __device__ __forceinline__ FeatWarp feat_warp(const FeatParams& p) {
 }
 
 // ------------------------------------------------------------------------------------------ forward
-template <int NC, int LD, int KF, int ACT, typename T>
+// MID: the fp32 state after every 16th step is also written to p.mid, for a backward whose inverse
+// chains then never exceed 16 steps.
+template <int NC, int LD, int KF, int ACT, typename T, bool MID = false>
 __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatParams p) {
   using G = FeatGeom<NC, LD, KF>;
   using F = ActForm<ACT>;
@@ -196,6 +203,17 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatPar
             X[r][q] = __ffma2_rn(A[r][q], f2(kC), __fmul2_rn(X[r][q], f2(kM)));
           }
         }
+        if constexpr (MID) {
+          const int done = rj * SEG + sj + 1;  // steps taken
+          if ((done & 15) == 0 && (done < NC || p.mid_end) && valid) {
+            float* mx = p.mid + (long long)(2 * (done / 16 - 1)) * p.bne;
+#pragma unroll
+            for (int r = 0; r < P; ++r) {
+              st_feat<KF, float>(mx + off[r], X[r]);
+              st_feat<KF, float>(mx + p.bne + off[r], A[r]);
+            }
+          }
+        }
       }
     }
     if (valid) {
@@ -278,7 +296,7 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
       const int blk = (int)(((long long)g + (long long)i * p.stride) % p.m);
       off[r] = ((b * p.N + (long long)blk * NC + i) * p.E) + fw.c * D + sub * KF;
       if (valid) {
-        if (!(SAVED && p.saved == 2)) {
+        if (!(SAVED && (p.saved == 2 || (p.saved == 3 && p.mid_end)))) {
           ld_feat<KF, T>(g_y + off[r], X[r]);
           ld_feat<KF, T>(g_ya + off[r], A[r]);
         }
@@ -294,8 +312,18 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
       // one body for every step: the row index of x_j inside a lane (rj) is a run-time value,
       // resolved by selects, so that the code stays small enough for the instruction cache
       if constexpr (SAVED) {
-        // the state after step j, exactly: the forward over steps 0..j from the saved input
-        if (j == NC / 2 - 1 || (j == NC - 1 && p.saved == 2)) {
+        if (p.saved == 3) {
+          // the state after step j as the forward stored it
+          if (((j + 1) & 15) == 0 && (j + 1 < NC || p.mid_end) && valid) {
+            const float* mx = p.mid + (long long)(2 * ((j + 1) / 16 - 1)) * p.bne;
+#pragma unroll
+            for (int r = 0; r < P; ++r) {
+              ld_feat<KF, float>(mx + off[r], X[r]);
+              ld_feat<KF, float>(mx + p.bne + off[r], A[r]);
+            }
+          }
+        } else if (j == NC / 2 - 1 || (j == NC - 1 && p.saved == 2)) {
+          // the state after step j, exactly: the forward over steps 0..j from the saved input
           const T* g_x = static_cast<const T*>(p.xin[0]);
           const T* g_xa = static_cast<const T*>(p.xin[1]);
           if (valid) {

@@ -24,6 +24,11 @@ cudaError_t launch_feat_bwds_n16(int d, int act, int dtype, const FeatParams& p,
                                  int* occ);
 cudaError_t launch_feat_bwds_n32(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
                                  int* occ);
+// the forward that also stores the state after every 16th step
+cudaError_t launch_feat_fwdm_n16(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+                                 int* occ);
+cudaError_t launch_feat_fwdm_n32(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+                                 int* occ);
 
 // groups a warp works on side by side for (n_cache, d); 0 if there is no kernel
 inline int feat_groups_per_warp(int n, int d) {

@@ -20,6 +20,10 @@ struct StageParams {
   const int* ctxlen;  // [B] context length per batch row, or null: every group takes all n steps
   const void* xin[2]; // bwd: the saved stage input (x, xa) or null
   int replay_all;     // bwd with xin: also the last segment starts from replayed values (y, ya are not read)
+  float* mid;         // fp32 states after every kSegment-th step (fwd: written if not null; bwd: read if not null):
+                      // state k, stream s at mid + (2k + s) * bne, in the element order of the activations
+  long long bne;      // elements per activation tensor
+  int mid_end;        // the state after the last step is stored / read too (y, ya are not read by the backward)
   long long B;
   long long groups;   // B * C * m
   int N, E, C, d, n, m, stride, ld_shift;  // LD = 1 << ld_shift
@@ -28,6 +32,9 @@ struct StageParams {
   int warps;
   uint32_t warp_floats;  // shared floats per warp
 };
+
+// longest chain of steps the backward rebuilds by the inverse when it has the stage input or stored states
+constexpr int kSegment = 16;
 
 __device__ __forceinline__ float act_rt(int act, float t) {
   switch (act) {
@@ -138,7 +145,21 @@ __global__ void __launch_bounds__(256) stage_fwd_kernel(const StageParams p, con
     }
     __syncwarp();
     const int steps = group_steps(p.ctxlen, b, g, n);
-    for (int j = 0; j < steps; ++j) stage_forward_step(p, act, X, A, xj, sim, Wi, Wj, j, lane);
+    for (int j = 0; j < steps; ++j) {
+      stage_forward_step(p, act, X, A, xj, sim, Wi, Wj, j, lane);
+      if (p.mid != nullptr && (j + 1) % kSegment == 0 && (j + 1 < steps || p.mid_end)) {
+        float* mx = p.mid + (long long)(2 * ((j + 1) / kSegment - 1)) * p.bne;
+        for (int i = li; i < n; i += LT) {
+          const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
+          const long long off = elem_off(b, pos, c * d, p.N, p.E);
+          for (int k = lk; k < d; k += LD) {
+            mx[off + k] = X[i * pitch + k];
+            mx[p.bne + off + k] = A[i * pitch + k];
+          }
+        }
+        __syncwarp();
+      }
+    }
     for (int i = li; i < n; i += LT) {
       const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
       const long long off = elem_off(b, pos, c * d, p.N, p.E);
@@ -156,7 +177,7 @@ __global__ void __launch_bounds__(256) stage_fwd_kernel(const StageParams p, con
 // With the stage INPUT saved as well (p.xin), the state at every kSegment-th step is rebuilt by
 // running the forward from the input, so that no inverse chain is longer than kSegment steps
 // (every inverse step grows earlier rounding by 1/m).
-constexpr int kSegment = 16;
+
 template <typename T>
 __global__ void __launch_bounds__(256) stage_bwd_kernel(const StageParams p, const int act) {
   extern __shared__ __align__(16) float sm[];
@@ -196,7 +217,7 @@ __global__ void __launch_bounds__(256) stage_bwd_kernel(const StageParams p, con
       const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
       const long long off = elem_off(b, pos, c * d, p.N, E);
       for (int k = lk; k < d; k += LD) {
-        if (!p.replay_all) {
+        if (!p.replay_all && !(p.mid != nullptr && p.mid_end)) {
           X[i * pitch + k] = Store<T>::ld(gy + off + k);
           A[i * pitch + k] = Store<T>::ld(gya + off + k);
         }
@@ -207,7 +228,20 @@ __global__ void __launch_bounds__(256) stage_bwd_kernel(const StageParams p, con
     __syncwarp();
     const int steps = group_steps(p.ctxlen, b, g, n);
     for (int j = steps - 1; j >= 0; --j) {
-      if (p.xin[0] != nullptr && (((j + 1) % kSegment == 0 && j + 1 < steps) || (j == steps - 1 && p.replay_all))) {
+      if (p.mid != nullptr) {
+        if ((j + 1) % kSegment == 0 && (j + 1 < steps || p.mid_end)) {  // the state after step j as the forward stored it
+          const float* mx = p.mid + (long long)(2 * ((j + 1) / kSegment - 1)) * p.bne;
+          for (int i = li; i < n; i += LT) {
+            const int pos = (int)(((long long)g + (long long)i * p.stride) % p.m) * n + i;
+            const long long off = elem_off(b, pos, c * d, p.N, E);
+            for (int k = lk; k < d; k += LD) {
+              X[i * pitch + k] = mx[off + k];
+              A[i * pitch + k] = mx[p.bne + off + k];
+            }
+          }
+          __syncwarp();
+        }
+      } else if (p.xin[0] != nullptr && (((j + 1) % kSegment == 0 && j + 1 < steps) || (j == steps - 1 && p.replay_all))) {
         // the state after step j, exactly: the forward over steps 0..j from the saved input
         const T* gxi = static_cast<const T*>(p.xin[0]);
         const T* gxa = static_cast<const T*>(p.xin[1]);

@@ -29,42 +29,59 @@ from . import ops
 MAX_INVERSE_STEPS = 16
 
 
-# What the per-stage operator keeps for its backward: "output" = the stage output only, as the
-# reference's NCNFunction does (the input is rebuilt by the reversible inverse over all n_cache
-# steps); "input" = the stage input as well (in a chain of stages it is the previous stage's saved
-# output, so it costs no memory), inverse chains of at most MAX_INVERSE_STEPS steps; "auto" =
-# "input" where the chain from the output would exceed MAX_INVERSE_STEPS steps.
+# What the per-stage operator keeps for its backward:
+#   "output"  the stage output only, as the reference's NCNFunction does (the input is rebuilt by the
+#             reversible inverse over all n_cache steps);
+#   "input"   the stage input as well: the backward replays the forward from it up to every 16th step, so
+#             no inverse chain exceeds MAX_INVERSE_STEPS steps.  In a chain of stages the input is the
+#             previous stage's saved output, so this costs no memory, but a third more backward time at 32 steps;
+#   "mid"     the forward also stores the fp32 state after every 16th step (8 bytes per element at 32 steps)
+#             and the backward restarts there: the accuracy of "input" at the speed of "output";
+#   "auto"    "output" where the chain from the output stays within MAX_INVERSE_STEPS steps (fp32 storage);
+#             beyond that "mid" for fp32 storage and "input" for bf16 storage (whose stored states
+#             would be many times the size of its activations).
 _STAGE_BACKWARD = "auto"
 
 
 def set_stage_backward(mode: str) -> str:
-    """Chooses what `NCNFunction` saves ("auto" | "output" | "input"); returns the previous choice."""
+    """Chooses what `NCNFunction` keeps ("auto" | "output" | "input" | "mid"); returns the previous choice."""
     global _STAGE_BACKWARD
-    if mode not in ("auto", "output", "input"):
+    if mode not in ("auto", "output", "input", "mid"):
         raise ValueError(f"unknown stage backward mode {mode!r}")
     prev, _STAGE_BACKWARD = _STAGE_BACKWARD, mode
     return prev
 
 
-def stage_saves_input(n_cache: int) -> bool:
-    if _STAGE_BACKWARD == "auto":
-        return n_cache > MAX_INVERSE_STEPS
-    return _STAGE_BACKWARD == "input"
+def stage_backward_plan(dtype, n_cache: int) -> str:
+    """-> "output" | "input" | "mid" for one stage of n_cache steps with this storage type."""
+    if _STAGE_BACKWARD != "auto":
+        return _STAGE_BACKWARD
+    if n_cache <= MAX_INVERSE_STEPS:
+        return "output"
+    return "mid" if dtype == torch.float32 else "input"
 
 
 class NCNFunction(torch.autograd.Function):
     """One stage (ncn_cuda/ncn_pytorch_wrapper_v2.py:9-50).  Saves the stage OUTPUT and rebuilds the
     input by the reversible inverse, as the reference does; for stages of more than
-    MAX_INVERSE_STEPS steps it keeps the stage input too (see set_stage_backward)."""
+    MAX_INVERSE_STEPS steps it keeps more (see set_stage_backward)."""
 
     @staticmethod
     def forward(ctx, x, xa, W, alpha, activation, n_cache, n_head, module_l):
-        yi, ya = ops.stage_fwd(x, xa, W, alpha, activation, n_cache, n_head, module_l)
-        ctx.saves_input = stage_saves_input(n_cache)
-        if ctx.saves_input:
-            ctx.save_for_backward(yi, ya, W, x, xa)
+        ctx.keep = stage_backward_plan(x.dtype, n_cache)
+        if ctx.keep == "mid":
+            yi, ya, mid = ops.stage_fwd_mid(x, xa, W, alpha, activation, n_cache, n_head, module_l)
+            if mid is None:
+                ctx.keep = "output"
+                ctx.save_for_backward(yi, ya, W)
+            else:
+                ctx.save_for_backward(yi, ya, W, mid)
         else:
-            ctx.save_for_backward(yi, ya, W)
+            yi, ya = ops.stage_fwd(x, xa, W, alpha, activation, n_cache, n_head, module_l)
+            if ctx.keep == "input":
+                ctx.save_for_backward(yi, ya, W, x, xa)
+            else:
+                ctx.save_for_backward(yi, ya, W)
         ctx.alpha = alpha
         ctx.activation = activation
         ctx.n_cache = n_cache
@@ -74,16 +91,16 @@ class NCNFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dyi, dya):
-        if ctx.saves_input:
+        cfg = (ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l)
+        if ctx.keep == "input":
             (yi, ya, W, x, xa) = ctx.saved_tensors
-            dx, dxa, dW = ops.stage_bwd_saved(
-                x, xa, yi, ya, dyi, dya, W, ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l
-            )
+            dx, dxa, dW = ops.stage_bwd_saved(x, xa, yi, ya, dyi, dya, W, *cfg)
+        elif ctx.keep == "mid":
+            (yi, ya, W, mid) = ctx.saved_tensors
+            dx, dxa, dW = ops.stage_bwd_mid(yi, ya, mid, dyi, dya, W, *cfg)
         else:
             (yi, ya, W) = ctx.saved_tensors
-            dx, dxa, dW = ops.stage_bwd(
-                yi, ya, dyi, dya, W, ctx.alpha, ctx.activation, ctx.n_cache, ctx.n_head, ctx.module_l
-            )
+            dx, dxa, dW = ops.stage_bwd(yi, ya, dyi, dya, W, *cfg)
         return dx, dxa, dW.to(W.dtype), None, None, None, None, None
 
 

@@ -140,6 +140,51 @@ def stage_bwd_saved(x, xa, y, ya, dy, dya, W, alpha, activation, n_cache, n_head
     return dx, dxa, dW
 
 
+def stage_fwd_mid(x, xa, W, alpha, activation, n_cache, n_head, module_l):
+    """Forward of one stage that also stores the fp32 state after every 16th step (ncn_stage_fwd_mid).
+    Returns (y, ya, mid); mid (opaque, or None where nothing needs storing) goes to stage_bwd_mid."""
+    lib = _lib.load()
+    _check_inputs(x, xa)
+    x, xa = x.contiguous(), xa.contiguous()
+    B, N, E = x.shape
+    W = _weights(W, 2 * E, x.device)
+    y, ya = torch.empty_like(x), torch.empty_like(xa)
+    dt = _dtype_code(x)
+    with torch.cuda.device(x.device):
+        nbytes = lib.ncn_stage_mid_bytes(B, N, E, n_cache, dt)
+        mid = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device) if nbytes else None
+        rc = lib.ncn_stage_fwd_mid(
+            x.data_ptr(), xa.data_ptr(), W.data_ptr(), y.data_ptr(), ya.data_ptr(),
+            mid.data_ptr() if mid is not None else None, nbytes, B, N, E, n_cache, n_head, module_l, float(alpha),
+            activation_code(activation), dt, _stream(),
+        )
+    _lib.check("ncn_stage_fwd_mid", rc)
+    return y, ya, mid
+
+
+def stage_bwd_mid(y, ya, mid, dy, dya, W, alpha, activation, n_cache, n_head, module_l):
+    """Backward of stage_fwd_mid: inverse chains of at most 16 steps, restarted at the stored states.
+    Returns (dx, dxa, dW[2E])."""
+    lib = _lib.load()
+    _check_inputs(y, ya, dy, dya)
+    y, ya, dy, dya = y.contiguous(), ya.contiguous(), dy.contiguous(), dya.contiguous()
+    B, N, E = y.shape
+    W = _weights(W, 2 * E, y.device)
+    dx, dxa = torch.empty_like(y), torch.empty_like(y)
+    dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
+    dt = _dtype_code(y)
+    with torch.cuda.device(y.device):
+        ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
+        rc = lib.ncn_stage_bwd_mid(
+            y.data_ptr(), ya.data_ptr(), mid.data_ptr() if mid is not None else None,
+            mid.numel() * 4 if mid is not None else 0, dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(),
+            dxa.data_ptr(), dW.data_ptr(), ws.data_ptr(), ws.numel(), B, N, E, n_cache, n_head, module_l, float(alpha),
+            activation_code(activation), dt, _stream(),
+        )
+    _lib.check("ncn_stage_bwd_mid", rc)
+    return dx, dxa, dW
+
+
 def _ctxlen(ctxlen, B, device) -> torch.Tensor:
     ctxlen = torch.as_tensor(ctxlen)
     if ctxlen.numel() != B:

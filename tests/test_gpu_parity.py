@@ -210,8 +210,9 @@ SAVED_CASES = [
 @pytest.mark.parametrize("B,N,E,C,n,l", SAVED_CASES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_stage_backward_with_saved_input(ncn, B, N, E, C, n, l, dtype):
-    """ncn_stage_bwd_saved: no inverse chain beyond 16 steps, so fp32 gradients of 32- and 64-step stages meet
-    1e-5; with bf16 storage the stage is replayed from its input, so the bound is the storage rounding."""
+    """ncn_stage_bwd_saved / ncn_stage_fwd_mid + ncn_stage_bwd_mid: no inverse chain beyond 16 steps, so fp32
+    gradients of 32- and 64-step stages meet 1e-5; with bf16 storage the stage is replayed from its input (or
+    starts from the stored fp32 end state), so the bound is the storage rounding."""
     torch.manual_seed(N + E + n)
     x, xa = torch.randn(B, N, E), torch.randn(B, N, E) * 0.3
     W = torch.randn(2 * E) * (0.5 / (E / C) ** 0.5)
@@ -228,23 +229,32 @@ def test_stage_backward_with_saved_input(ncn, B, N, E, C, n, l, dtype):
     tol = TOL32 if dtype == torch.float32 else TOLBF
     errs = [O.rel_err(dx.float(), xr.grad), O.rel_err(dxa.float(), xar.grad), O.rel_err(dW, Wr.grad)]
     assert max(errs) < tol, errs
-    # the operator picks this path by itself for stages of more than 16 steps ...
-    prev = ncn.set_stage_backward("auto")
-    try:
-        xg, xag, Wg = xd.clone().requires_grad_(), xad.clone().requires_grad_(), Wd.clone().requires_grad_()
-        yy, yya = ncn.fused_ncn_cuda_v2(xg, xag, Wg, 0.9, 0, n, C, l)
-        torch.autograd.backward([yy, yya], [dev(dy).to(dtype), dev(dya).to(dtype)])
-        if n > 16:
-            assert torch.equal(xg.grad, dx) and torch.equal(Wg.grad, dW)
-        # ... and "output" is the reference's contract (nothing but the stage output is kept)
-        ncn.set_stage_backward("output")
-        xo, xao, Wo = xd.clone().requires_grad_(), xad.clone().requires_grad_(), Wd.clone().requires_grad_()
-        yy, yya = ncn.fused_ncn_cuda_v2(xo, xao, Wo, 0.9, 0, n, C, l)
-        torch.autograd.backward([yy, yya], [dev(dy).to(dtype), dev(dya).to(dtype)])
-        o_errs = [O.rel_err(xo.grad.float(), xr.grad), O.rel_err(xao.grad.float(), xar.grad), O.rel_err(Wo.grad, Wr.grad)]
-        print("\nsaved-input backward", (B, N, E, C, n, l), str(dtype), "errors", errs, "from the output alone", o_errs)
-    finally:
-        ncn.set_stage_backward(prev)
+    # the same accuracy from states the forward stored (no replay)
+    ym, yam, mid = ncn.ops.stage_fwd_mid(xd, xad, Wd, 0.9, 0, n, C, l)
+    assert torch.equal(ym, y) and torch.equal(yam, ya)
+    assert (mid is None) == (dtype == torch.float32 and n <= 16)
+    mdx, mdxa, mdW = ncn.ops.stage_bwd_mid(y, ya, mid, dev(dy).to(dtype), dev(dya).to(dtype), Wd, 0.9, 0, n, C, l)
+    ncn.ops.device_status()
+    m_errs = [O.rel_err(mdx.float(), xr.grad), O.rel_err(mdxa.float(), xar.grad), O.rel_err(mdW, Wr.grad)]
+    assert max(m_errs) < tol, m_errs
+    # what the operator does by itself, and the reference's contract ("output": nothing but the stage output is kept)
+    got = {}
+    for keep in ("auto", "input", "mid", "output"):
+        prev = ncn.set_stage_backward(keep)
+        try:
+            xg, xag, Wg = xd.clone().requires_grad_(), xad.clone().requires_grad_(), Wd.clone().requires_grad_()
+            yy, yya = ncn.fused_ncn_cuda_v2(xg, xag, Wg, 0.9, 0, n, C, l)
+            torch.autograd.backward([yy, yya], [dev(dy).to(dtype), dev(dya).to(dtype)])
+            got[keep] = (xg.grad, xag.grad, Wg.grad)
+        finally:
+            ncn.set_stage_backward(prev)
+    assert torch.equal(got["input"][0], dx) and torch.equal(got["input"][2], dW)
+    assert torch.equal(got["mid"][0], mdx) and torch.equal(got["mid"][2], mdW)
+    auto = "output" if (n <= 16) else ("mid" if dtype == torch.float32 else "input")
+    assert torch.equal(got["auto"][0], got[auto][0]) and torch.equal(got["auto"][2], got[auto][2])
+    o_errs = [O.rel_err(a.float(), b) for a, b in zip(got["output"], (xr.grad, xar.grad, Wr.grad))]
+    print("\nstage backward", (B, N, E, C, n, l), str(dtype), "input kept", errs, "states stored", m_errs,
+          "from the output alone", o_errs)
     ncn.ops.device_status()
 
 
