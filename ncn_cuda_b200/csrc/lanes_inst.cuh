@@ -10,7 +10,8 @@ static cudaError_t launch_one(const LaneParams& p, int grid, int threads, size_t
 #if NCN_NG == 4
   if (p.pipelined) {  // two half-rows per thread, half a stage apart (ncn_lanes_pipe.cuh)
     auto kp = lanep_bwd_kernel<NCN_NG, ACT, T, kLaneThreads, kLaneBwdBlocks>;
-    cudaError_t ep = cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemGrant granted_p;
+    cudaError_t ep = grant_smem(granted_p, kp, smem);
     if (ep != cudaSuccess) return ep;
     if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kp, threads, smem);
     kp<<<grid, threads, smem, st>>>(p);
@@ -21,7 +22,8 @@ static cudaError_t launch_one(const LaneParams& p, int grid, int threads, size_t
 #else
   auto k = lane_fwd_kernel<NCN_NG, ACT, T, kLaneThreads, kLaneFwdBlocks>;
 #endif
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemGrant granted;
+  cudaError_t e = grant_smem(granted, k, smem);
   if (e != cudaSuccess) return e;
   if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, smem);
   k<<<grid, threads, smem, st>>>(p);

@@ -666,11 +666,34 @@ static int plan_generic(K kernel, bool bwd, int64_t groups, int n, int d, int E,
   g.warps = warps;
   g.warp_floats = (uint32_t)wf;
   g.smem = (size_t)(wf * 4 * warps);
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
-  if (e != cudaSuccess) return cuda_fail(e);
-  int occ = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, warps * 32, g.smem);
-  if (e != cudaSuccess) return cuda_fail(e);
+  // The occupancy is remembered per (kernel, device, CTA shape); the shared-memory attribute is only ever raised
+  // (a later, smaller request must not lower what an earlier, larger launch shape still needs).
+  struct Seen { const void* k; int dev, warps; size_t smem; int occ; };
+  struct Grant { const void* k; int dev; size_t bytes; };
+  static std::mutex mu;
+  static std::vector<Seen> seen;
+  static std::vector<Grant> grants;
+  int occ = -1;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (const Seen& q : seen)
+      if (q.k == (const void*)kernel && q.dev == dev.dev && q.warps == warps && q.smem == g.smem) { occ = q.occ; break; }
+  }
+  if (occ < 0) {
+    std::lock_guard<std::mutex> lk(mu);
+    Grant* gr = nullptr;
+    for (Grant& q : grants)
+      if (q.k == (const void*)kernel && q.dev == dev.dev) { gr = &q; break; }
+    if (gr == nullptr || gr->bytes < g.smem) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
+      if (e != cudaSuccess) return cuda_fail(e);
+      if (gr) gr->bytes = g.smem; else grants.push_back(Grant{(const void*)kernel, dev.dev, g.smem});
+    }
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, warps * 32, g.smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (seen.size() >= 64) seen.clear();
+    seen.push_back(Seen{(const void*)kernel, dev.dev, warps, g.smem, occ});
+  }
   if (occ < 1) return NCN_ERR_SMEM;
   if (occ > 8) occ = 8;
   long long grid = (groups + warps - 1) / warps;
@@ -769,10 +792,26 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
   int wpc = kFeatWarps;
   while (wpc > 1 && want_warps < (long long)dev.sms * wpc) wpc /= 2;
   const int threads = wpc * 32;
-  int occ = 0;
-  cudaError_t e = fn(d, act, dtype, p, 0, threads, nullptr, &occ);
-  if (e == cudaErrorNotSupported) return NCN_ERR_UNSUPPORTED;
-  if (e != cudaSuccess) return cuda_fail(e);
+  // resident CTAs per SM of this kernel: asked once per (kernel, device, CTA size)
+  struct Seen { FeatLaunchFn fn; int d, act, dtype, threads, dev, occ; };
+  static std::mutex mu;
+  static std::vector<Seen> seen;
+  int occ = -1;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (const Seen& q : seen)
+      if (q.fn == fn && q.d == d && q.act == act && q.dtype == dtype && q.threads == threads && q.dev == dev.dev) { occ = q.occ; break; }
+  }
+  cudaError_t e = cudaSuccess;
+  if (occ < 0) {
+    occ = 0;
+    e = fn(d, act, dtype, p, 0, threads, nullptr, &occ);
+    if (e == cudaErrorNotSupported) return NCN_ERR_UNSUPPORTED;
+    if (e != cudaSuccess) return cuda_fail(e);
+    std::lock_guard<std::mutex> lk(mu);
+    if (seen.size() >= 128) seen.clear();
+    seen.push_back(Seen{fn, d, act, dtype, threads, dev.dev, occ});
+  }
   if (occ < 1) return NCN_ERR_UNSUPPORTED;
   if (occ > 32) occ = 32;
   // one warp per (head, unit) at most, a whole number of warps per head

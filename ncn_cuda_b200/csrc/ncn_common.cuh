@@ -12,6 +12,24 @@
 
 namespace ncn {
 
+// Host side: cudaFuncSetAttribute(MaxDynamicSharedMemorySize) only when this process has not yet granted the
+// kernel at least `smem` bytes on the current device; repeated on every launch the call costs about a
+// microsecond.  One SmemGrant per kernel (a function-local static of its launcher); races between threads
+// are benign (at worst one more call).
+struct SmemGrant {
+  int bytes[16] = {};
+};
+template <typename K>
+inline cudaError_t grant_smem(SmemGrant& g, K kernel, size_t smem) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+  if (dev >= 0 && dev < 16 && g.bytes[dev] >= (int)smem) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess && dev >= 0 && dev < 16) g.bytes[dev] = (int)smem;
+  return e;
+}
+
+
 // The two-stream mixing constant is a literal 0.9 everywhere in the reference
 // (torch_ref/ncn_pytorch.py:89); (1 - 0.9) is formed in double and rounded to fp32 there.
 constexpr float kM = 0.9f;

@@ -19,7 +19,8 @@ static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t
   if (p.variant == 2) {
     if constexpr (NCN_NG <= 8) {
       auto kd = pair_bwd_dual_kernel<NCN_NG, ACT, T, NCN_CFG::threads / 2>;
-      cudaError_t ed = cudaFuncSetAttribute(kd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      static SmemGrant granted_d;
+      cudaError_t ed = grant_smem(granted_d, kd, smem);
       if (ed != cudaSuccess) return ed;
       if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kd, threads, smem);
       kd<<<grid, threads, smem, st>>>(p);
@@ -30,7 +31,8 @@ static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t
   }
   if (p.variant == 1) {
     auto kw = pair_bwd_wide_kernel<NCN_NG, ACT, T, NCN_CFG::threads>;
-    cudaError_t ew = cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemGrant granted_w;
+    cudaError_t ew = grant_smem(granted_w, kw, smem);
     if (ew != cudaSuccess) return ew;
     if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kw, threads, smem);
     kw<<<grid, threads, smem, st>>>(p);
@@ -40,7 +42,8 @@ static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t
 #ifndef NCN_BWD
   if (p.variant == 2) {
     auto kd = pair_fwd_dual_kernel<NCN_NG, ACT, T, NCN_CFG::threads / 2, (NCN_NG <= 8 ? 4 : 2)>;
-    cudaError_t ed = cudaFuncSetAttribute(kd, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemGrant granted_fd;
+    cudaError_t ed = grant_smem(granted_fd, kd, smem);
     if (ed != cudaSuccess) return ed;
     if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kd, threads, smem);
     kd<<<grid, threads, smem, st>>>(p);
@@ -48,7 +51,8 @@ static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t
   }
 #endif
   auto k = NCN_KERNEL<NCN_NG, ACT, T, NCN_CFG::threads, NCN_CFG::min_blocks>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemGrant granted;
+  cudaError_t e = grant_smem(granted, k, smem);
   if (e != cudaSuccess) return e;
   if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, smem);
   k<<<grid, threads, smem, st>>>(p);

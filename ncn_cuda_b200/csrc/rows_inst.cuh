@@ -17,7 +17,8 @@ namespace ncn {
 template <int ACT, typename T>
 static cudaError_t launch_one(const RowsParams& p, int grid, int threads, size_t smem, cudaStream_t st, int* occ) {
   auto k = NCN_KERNEL<NCN_NG, ACT, T, NCN_MAXT>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemGrant granted;
+  cudaError_t e = grant_smem(granted, k, smem);
   if (e != cudaSuccess) return e;
   if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, smem);
   k<<<grid, threads, smem, st>>>(p);

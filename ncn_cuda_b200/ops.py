@@ -5,6 +5,7 @@ kernels of libncn_b200.so on the current stream and returns torch tensors.
 """
 from __future__ import annotations
 
+import contextlib
 from typing import Optional, Tuple
 
 import torch
@@ -49,6 +50,17 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def _on(device):
+    """Context in which `device` is the current CUDA device; free when it already is (the switch
+    of torch.cuda.device costs several microseconds per call even as a no-op)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _weights(W: torch.Tensor, numel: int, device) -> torch.Tensor:
     W = W.detach()
     if W.dtype != torch.float32 or not W.is_contiguous() or W.device != device:
@@ -71,7 +83,7 @@ def _workspace(lib, device, B, N, E, n_cache, n_head, L, dt) -> torch.Tensor:
 def net_supported(x: torch.Tensor, n_cache: int, n_head: int, L: int, flags: int = 0, ckpt_every: int = 0) -> bool:
     lib = _lib.load()
     B, N, E = x.shape
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         return bool(lib.ncn_net_supported(B, N, E, n_cache, n_head, L, _dtype_code(x), flags, ckpt_every))
 
 
@@ -82,7 +94,7 @@ def stage_fwd(x, xa, W, alpha, activation, n_cache, n_head, module_l) -> Tuple[t
     B, N, E = x.shape
     W = _weights(W, 2 * E, x.device)
     y, ya = torch.empty_like(x), torch.empty_like(xa)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = lib.ncn_stage_fwd(
             x.data_ptr(), xa.data_ptr(), W.data_ptr(), y.data_ptr(), ya.data_ptr(), B, N, E, n_cache, n_head,
             module_l, float(alpha), activation_code(activation), _dtype_code(x), _stream(),
@@ -103,7 +115,7 @@ def stage_bwd(y, ya, dy, dya, W, alpha, activation, n_cache, n_head, module_l, w
     xar = torch.empty_like(y) if want_inputs else None
     dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
     dt = _dtype_code(y)
-    with torch.cuda.device(y.device):
+    with _on(y.device):
         ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
         rc = lib.ncn_stage_bwd(
             y.data_ptr(), ya.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(), dxa.data_ptr(),
@@ -129,7 +141,7 @@ def stage_bwd_saved(x, xa, y, ya, dy, dya, W, alpha, activation, n_cache, n_head
     dx, dxa = torch.empty_like(y), torch.empty_like(y)
     dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
     dt = _dtype_code(y)
-    with torch.cuda.device(y.device):
+    with _on(y.device):
         ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
         rc = lib.ncn_stage_bwd_saved(
             x.data_ptr(), xa.data_ptr(), y.data_ptr(), ya.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(),
@@ -150,7 +162,7 @@ def stage_fwd_mid(x, xa, W, alpha, activation, n_cache, n_head, module_l):
     W = _weights(W, 2 * E, x.device)
     y, ya = torch.empty_like(x), torch.empty_like(xa)
     dt = _dtype_code(x)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         nbytes = lib.ncn_stage_mid_bytes(B, N, E, n_cache, dt)
         mid = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device) if nbytes else None
         rc = lib.ncn_stage_fwd_mid(
@@ -173,7 +185,7 @@ def stage_bwd_mid(y, ya, mid, dy, dya, W, alpha, activation, n_cache, n_head, mo
     dx, dxa = torch.empty_like(y), torch.empty_like(y)
     dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
     dt = _dtype_code(y)
-    with torch.cuda.device(y.device):
+    with _on(y.device):
         ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
         rc = lib.ncn_stage_bwd_mid(
             y.data_ptr(), ya.data_ptr(), mid.data_ptr() if mid is not None else None,
@@ -202,7 +214,7 @@ def stage_fwd_ctx(x, xa, W, ctxlen, alpha, activation, n_cache, n_head, module_l
     W = _weights(W, 2 * E, x.device)
     cl = _ctxlen(ctxlen, B, x.device)
     y, ya = torch.empty_like(x), torch.empty_like(xa)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = lib.ncn_stage_fwd_ctx(
             x.data_ptr(), xa.data_ptr(), W.data_ptr(), cl.data_ptr(), y.data_ptr(), ya.data_ptr(), B, N, E, n_cache, n_head,
             module_l, float(alpha), activation_code(activation), _dtype_code(x), _stream(),
@@ -222,7 +234,7 @@ def stage_bwd_ctx(y, ya, dy, dya, W, ctxlen, alpha, activation, n_cache, n_head,
     dx, dxa = torch.empty_like(y), torch.empty_like(y)
     dW = torch.empty(2 * E, dtype=torch.float32, device=y.device)
     dt = _dtype_code(y)
-    with torch.cuda.device(y.device):
+    with _on(y.device):
         ws = _workspace(lib, y.device, B, N, E, n_cache, n_head, 1, dt)
         rc = lib.ncn_stage_bwd_ctx(
             y.data_ptr(), ya.data_ptr(), dy.data_ptr(), dya.data_ptr(), W.data_ptr(), cl.data_ptr(), dx.data_ptr(),
@@ -244,7 +256,7 @@ def net_fwd(x, xa, W, alpha, activation, n_cache, n_head, first_module=0, ckpt_e
     W = _weights(W, L * 2 * E, x.device)
     y, ya = torch.empty_like(x), torch.empty_like(xa)
     ckpt = None
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         flags = (NCN_RESIDUAL if residual else 0) | (NCN_TAPE if tape else 0)
         nbytes = lib.ncn_ckpt_bytes(B, N, E, L, ckpt_every, flags)
         if nbytes:
@@ -284,7 +296,7 @@ def net_bwd(s0, s1, dy, dya, W, alpha, activation, n_cache, n_head, first_module
     dW = dW_out if accumulate else torch.empty(L, 2 * E, dtype=torch.float32, device=dy.device)
     flags = (NCN_RECOMPUTE if recompute else 0) | (NCN_RESIDUAL if residual else 0) | (NCN_TAPE if tape else 0)
     dt = _dtype_code(dy)
-    with torch.cuda.device(dy.device):
+    with _on(dy.device):
         ws = _workspace(lib, dy.device, B, N, E, n_cache, n_head, L, dt)
         rc = lib.ncn_net_bwd(
             s0.data_ptr() if s0 is not None else None, s1.data_ptr() if s1 is not None else None, dy.data_ptr(), dya.data_ptr(), W.data_ptr(), dx.data_ptr(), dxa.data_ptr(),
