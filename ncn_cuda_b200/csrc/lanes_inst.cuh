@@ -20,6 +20,17 @@ static cudaError_t launch_one(const LaneParams& p, int grid, int threads, size_t
 #endif
   auto k = lane_bwd_kernel<NCN_NG, ACT, T, kLaneThreads, kLaneBwdBlocks>;
 #else
+#if NCN_NG == 4
+  if (p.pipelined) {  // (A/B runs only: measured slower than lane_fwd_kernel)
+    auto kp = lanep_fwd_kernel<NCN_NG, ACT, T, kLaneThreads, kLaneBwdBlocks>;
+    static SmemGrant granted_pf;
+    cudaError_t ep = grant_smem(granted_pf, kp, smem);
+    if (ep != cudaSuccess) return ep;
+    if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, kp, threads, smem);
+    kp<<<grid, threads, smem, st>>>(p);
+    return cudaGetLastError();
+  }
+#endif
   auto k = lane_fwd_kernel<NCN_NG, ACT, T, kLaneThreads, kLaneFwdBlocks>;
 #endif
   static SmemGrant granted;

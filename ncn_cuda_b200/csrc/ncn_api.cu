@@ -60,6 +60,7 @@ static int get_dev(DevInfo& out) {
 struct EnvSwitches {
   bool exact_tanh, no_pair, no_feat, bwd_wide_off, bwd_dual_off, fwd_dual_off, lanes_off, lanes_pipe_off;
   int fwd_threads, bwd_threads, nbuf, lane_rows;
+  bool lanes_pipe_fwd;   // NCN_LANES_PIPE_FWD=1: the pipelined forward (measured slower; kept for A/B runs)
   bool test_short_wait;  // NCN_TEST_SHORT_WAIT=1: the lane forward gives up its first wait (tests of that path)
 };
 static EnvSwitches read_env_switches() {
@@ -84,6 +85,7 @@ static EnvSwitches read_env_switches() {
   v.bwd_threads = num("NCN_BWD_THREADS");
   v.nbuf = num("NCN_NBUF");
   v.lane_rows = num("NCN_LANE_ROWS");
+  v.lanes_pipe_fwd = is("NCN_LANES_PIPE_FWD", '1');
   v.test_short_wait = is("NCN_TEST_SHORT_WAIT", '1');
   return v;
 }
@@ -485,9 +487,10 @@ static bool lane_layout(bool bwd, int N, int n, int L, int dtype, int flags, int
 // Pipelined backward (n = 4, ncn_lanes_pipe.cuh): a thread runs the two halves of its row half a
 // stage apart; every shift goes by shuffles + halo, and the halo lives in the tile buffer.  Needs
 // every change of stride to stay within a warp's reach: 3 * 2^e / 2 <= 24 lanes, i.e. e <= 4.
-static bool lanep_layout(int N, int L, int dtype, int flags, int n_ck, int R, int tpr, int e_need, uint32_t limit,
+static bool lanep_layout(bool bwd, int N, int L, int dtype, int flags, int n_ck, int R, int tpr, int e_need, uint32_t limit,
                          LanePlan& pl) {
   if (e_need > 4) return false;
+  const int NS = bwd ? 4 : 2;  // streams a thread holds
   const int w = dtype == DT_BF16 ? 2 : 4;
   const bool residual = (flags & F_RESIDUAL) != 0;
   const uint64_t RN = (uint64_t)R * N;
@@ -495,8 +498,8 @@ static bool lanep_layout(int N, int L, int dtype, int flags, int n_ck, int R, in
   const int warps = threads / 32;
   const int kmax = 3 * (e_need >= 0 ? (1 << e_need) : 0);
   const uint32_t so = (uint32_t)((4 * (kmax + 2) + 7) / 8 * 8);  // bytes per (stream, offset) region
-  pl.halo_warp_bytes = 4 * 3 * so;
-  uint64_t work = 4 * RN * w;
+  pl.halo_warp_bytes = NS * 3 * so;
+  uint64_t work = NS * RN * w;
   const uint64_t halo = (uint64_t)2 * warps * pl.halo_warp_bytes;  // two half-row "warps" per warp
   if (halo > work) work = halo;
   uint64_t off = 0;
@@ -504,7 +507,7 @@ static bool lanep_layout(int N, int L, int dtype, int flags, int n_ck, int R, in
   pl.off_work = take(work);
   pl.off_halo = pl.off_work;
   pl.off_res = residual ? take(RN * w) : pl.off_work;
-  pl.off_ckpt = take(n_ck ? (uint64_t)n_ck * RN * 8 : 16);
+  pl.off_ckpt = take(bwd && n_ck ? (uint64_t)n_ck * RN * 8 : 16);  // (the forward stores its states straight to global memory)
   pl.off_red = take((uint64_t)2 * L * warps * 4);
   pl.off_w = take((uint64_t)16 * L);
   pl.off_bar = take(32);
@@ -566,13 +569,13 @@ static int plan_lanes(bool bwd, int64_t B, int64_t N, int64_t E, int n, int C, i
   int rc = NCN_ERR_UNSUPPORTED;
   LanePlan best;
   bool have_pipe = false;
-  if (bwd && n == 4 && lanep_enabled()) {
+  if (n == 4 && (bwd ? lanep_enabled() : env_switches().lanes_pipe_fwd)) {
     LanePlan trial;
-    if (lanep_layout((int)N, L, dtype, flags, n_ck, R, tpr, e_need, (uint32_t)dev.smem_optin, trial)) {
+    if (lanep_layout(bwd, (int)N, L, dtype, flags, n_ck, R, tpr, e_need, (uint32_t)dev.smem_optin, trial)) {
       int occ = 0;
       LaneParams dummy{};
       dummy.pipelined = 1;
-      cudaError_t e = lane_fn(n, true)(act, dtype, dummy, 0, trial.threads, trial.smem, nullptr, &occ);
+      cudaError_t e = lane_fn(n, bwd)(act, dtype, dummy, 0, trial.threads, trial.smem, nullptr, &occ);
       if (e != cudaSuccess) return cuda_fail(e);
       if (occ >= 1) {
         trial.occ = occ > want_occ ? want_occ : occ;
