@@ -113,3 +113,57 @@ def test_sweep(ncn, monkeypatch, k, B, N, n, l0, L, act, dtype, mode):
         assert max(errs2[:2]) < tol_f, (errs2, "forward, NCN_LANES=0")
         if tol_b is not None:
             assert max(errs2[2:]) < tol_b, (errs2, "backward, NCN_LANES=0")
+
+
+def _stage_cases():
+    rng = random.Random(777)
+    out = []
+    for k in range(40):
+        d = rng.choice([1, 2, 3, 4, 8, 16, 32, 64, 128, 40])
+        C = rng.choice([1, 1, 2, 3, 4])
+        n = rng.choice([2, 4, 8, 16, 32])
+        while n * d > 2048:
+            n //= 2
+        m = rng.choice([3, 8, 9, 16, 33])
+        B = rng.choice([1, 2, 5])
+        l = rng.randint(0, 4)
+        act = rng.choice(["tanh", "tanh", "linear", "sigmoid", "leaky-relu"])
+        dtype = rng.choice([torch.float32, torch.float32, torch.bfloat16])
+        out.append((k, B, n * m, d * C, C, n, l, act, dtype))
+    return out
+
+
+@pytest.mark.parametrize("k,B,N,E,C,n,l,act,dtype", _stage_cases())
+def test_sweep_stage(ncn, k, B, N, E, C, n, l, act, dtype):
+    """The per-stage operator (any number of features and heads) through autograd, as the reference's modules call
+    it: which kernel serves a call (register-tiled, shared-memory, fused one-feature) and what it keeps for the
+    backward follows from the shape and the storage type."""
+    g = torch.Generator().manual_seed(5000 + k)
+    x = torch.randn(B, N, E, generator=g)
+    xa = torch.randn(B, N, E, generator=g) * 0.3
+    W = torch.randn(2 * E, generator=g) * (0.5 / (E / C) ** 0.5)
+    dy, dya = torch.randn(B, N, E, generator=g), torch.randn(B, N, E, generator=g)
+    if dtype != torch.float32:
+        x, xa, dy, dya = (t.bfloat16().float() for t in (x, xa, dy, dya))
+    xr, xar, Wr = x.clone().requires_grad_(), xa.clone().requires_grad_(), W.clone().requires_grad_()
+    ry, rya = O.stage_forward(xr, xar, Wr, 0.9, act, n, C, l)
+    torch.autograd.backward([ry, rya], [dy, dya])
+    xd, xad, Wd = x.cuda().to(dtype).requires_grad_(), xa.cuda().to(dtype).requires_grad_(), W.cuda().requires_grad_()
+    y, ya = ncn.fused_ncn_cuda_v2(xd, xad, Wd, 0.9, ncn.ops.ACTIVATION_CODES[act], n, C, l)
+    torch.autograd.backward([y, ya], [dy.cuda().to(dtype), dya.cuda().to(dtype)])
+    ncn.ops.device_status()
+    tol = TOL32 if dtype == torch.float32 else TOLBF
+    # bf16 storage: a weight gradient is a sum of a few hundred rounded terms that largely cancel at these sizes
+    # (one or two rows), so its error relative to the result is larger than that of the activations: 3e-2
+    tol_w = tol if dtype == torch.float32 else 3e-2
+    errs = [O.rel_err(a.float(), b) for a, b in
+            zip((y, ya, xd.grad, xad.grad, Wd.grad), (ry.detach(), rya.detach(), xr.grad, xar.grad, Wr.grad))]
+    if act == "leaky-relu":
+        # a kink, as for relu: a value within rounding of it (storage rounding with bf16) may land on its other side,
+        # so the gradients are compared in the mean: 1e-3 (fp32), 5e-2 (bf16, where the rebuilt input carries the
+        # rounding of the stored output)
+        errs[2:] = [float((a.double().cpu() - b.double()).norm() / b.double().norm().clamp_min(1e-30))
+                    for a, b in zip((xd.grad.float(), xad.grad.float(), Wd.grad), (xr.grad, xar.grad, Wr.grad))]
+        assert max(errs[:2]) < tol and max(errs[2:]) < (1e-3 if dtype == torch.float32 else 5e-2), errs
+    else:
+        assert max(errs[:4]) < tol and errs[4] < tol_w, errs
