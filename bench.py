@@ -65,7 +65,7 @@ WORKLOADS = {
 
 # Workloads measured for a few steps after the headline one in a default run (one GPU: all of them;
 # several GPUs: the stack, which is the configuration quoted at 1/2/4/8 GPUs).
-EXTRA_1GPU = ["cfg2_linear", "cfg4", "cfg3", "cfg5", "cfg1"]
+EXTRA_1GPU = ["cfg2_linear", "cfg4", "cfg3", "cfg5", "cfg1", "ref_e128", "ref_e128_mid"]
 EXTRA_NGPU = ["cfg5"]
 
 # DRAM bytes per element moved by the backward kernel in one launch (dram__bytes_read.sum +

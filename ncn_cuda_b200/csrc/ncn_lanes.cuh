@@ -226,6 +226,60 @@ __device__ __forceinline__ void exchange_shfl(float2 (&V)[NS][G / 2][NG], uint32
   constexpr int D = 1 << E;
   constexpr int HS = lane_halo_floats(NG, E);  // floats per stream
   constexpr int CH = 32 * G;                   // blocks per warp
+  if constexpr (E == 0 && G == 2) {
+    // One pair per thread and shifts by k = o blocks.  The pair is published whole (for odd k one value more than
+    // the neighbour reads); odd shifts swap the halves of a pair: x <- y of lane +- (k-1)/2, y <- x of lane +- (k+1)/2.
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+#pragma unroll
+      for (int o = 1; o < NG; ++o) {
+        const uint32_t reg = halo_pub + 4u * (uint32_t)(s * HS + lane_halo_pair_base(o));
+        if (!UP) {
+          sts64_if(2 * lane < o, reg + 8u * (uint32_t)lane, V[s][0][o].x, V[s][0][o].y);
+        } else {
+          const int kb = (CH - o) & ~1;  // first published block, rounded down to a pair
+          sts64_if(2 * lane >= kb, reg + 4u * (uint32_t)(2 * lane - kb), V[s][0][o].x, V[s][0][o].y);
+        }
+      }
+    }
+    cta_sync();
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+#pragma unroll
+      for (int o = 1; o < NG; ++o) {
+        const uint32_t reg = halo_nbr + 4u * (uint32_t)(s * HS + lane_halo_pair_base(o));
+        const float2 v = V[s][0][o];
+        float2 n;
+        if (o & 1) {
+          const int qa = o >> 1, qb = (o + 1) >> 1;
+          if (!UP) {
+            n.x = qa > 0 ? __shfl_down_sync(0xffffffffu, v.y, qa) : v.y;
+            n.y = __shfl_down_sync(0xffffffffu, v.x, qb);
+            lds32_if(lane + qa >= 32, reg + 4u * (uint32_t)(2 * lane + o - CH), n.x);
+            lds32_if(lane + qb >= 32, reg + 4u * (uint32_t)(2 * lane + o + 1 - CH), n.y);
+          } else {
+            n.x = __shfl_up_sync(0xffffffffu, v.y, qb);
+            n.y = qa > 0 ? __shfl_up_sync(0xffffffffu, v.x, qa) : v.x;
+            lds32_if(lane < qb, reg + 4u * (uint32_t)(2 * lane + 1), n.x);  // the lower warp's area starts at block CH - 1 - o
+            lds32_if(lane < qa, reg + 4u * (uint32_t)(2 * lane + 2), n.y);
+          }
+        } else {
+          const int q = o >> 1;
+          if (!UP) {
+            n.x = __shfl_down_sync(0xffffffffu, v.x, q);
+            n.y = __shfl_down_sync(0xffffffffu, v.y, q);
+            lds64_if(lane + q >= 32, reg + 8u * (uint32_t)(lane + q - 32), n);
+          } else {
+            n.x = __shfl_up_sync(0xffffffffu, v.x, q);
+            n.y = __shfl_up_sync(0xffffffffu, v.y, q);
+            lds64_if(lane < q, reg + 8u * (uint32_t)lane, n);
+          }
+        }
+        V[s][0][o] = n;
+      }
+    }
+    return;
+  }
   const int c0 = G * lane;
   // ---- publish what the neighbouring warp will want
 #pragma unroll

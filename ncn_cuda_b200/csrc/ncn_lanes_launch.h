@@ -27,8 +27,17 @@ struct LaneParams {
 __host__ __device__ constexpr int lane_groups(int ng) { return ng == 2 ? 8 : ng == 4 ? 4 : 2; }
 // largest log2 |stride difference| the shuffle exchange is compiled for
 __host__ __device__ constexpr int lane_ea_cap(int ng) { return ng == 2 ? 6 : ng == 4 ? 4 : 2; }
-// halo floats per warp and stream for a stride difference of 2^e: sum over offsets o of o 2^e
-__host__ __device__ constexpr int lane_halo_floats(int ng, int e) { return (1 << e) * ng * (ng - 1) / 2; }
+// halo floats per warp and stream for a stride difference of 2^e: sum over offsets o of o 2^e (for e = 0 every
+// offset's region is rounded up to whole pairs)
+__host__ __device__ constexpr int lane_halo_floats(int ng, int e) {
+  return e == 0 ? ng * (ng - 1) / 2 + ng / 2 : (1 << e) * ng * (ng - 1) / 2;
+}
+// first float of offset o's region when the regions hold whole pairs (e = 0): sum over o' < o of o' rounded up to even
+__host__ __device__ constexpr int lane_halo_pair_base(int o) {
+  int b = 0;
+  for (int q = 1; q < o; ++q) b += (q + 1) & ~1;
+  return b;
+}
 
 // Block size the kernels are compiled for, and the CTAs per SM their register budget allows.
 constexpr int kLaneThreads = 256;
