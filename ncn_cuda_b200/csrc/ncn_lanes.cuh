@@ -425,16 +425,22 @@ __device__ __forceinline__ void lane_exchange(float2 (&V)[NS][G / 2][NG], int de
   const uint32_t pub = bufa + (uint32_t)h.warp * h.warp_bytes;
   const uint32_t nbr = bufa + (uint32_t)(up ? h.warp_dn : h.warp_up) * h.warp_bytes;
   constexpr int CAP = lane_ea_cap(NG);
-  switch (e) {
-    case 0: if (up) exchange_shfl<NG, G, NS, 0, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 0, false>(V, pub, nbr, lane); break;
-    case 1: if (up) exchange_shfl<NG, G, NS, 1, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 1, false>(V, pub, nbr, lane); break;
-    case 2: if (up) exchange_shfl<NG, G, NS, 2, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 2, false>(V, pub, nbr, lane); break;
-    case 3: if constexpr (CAP >= 3) { if (up) exchange_shfl<NG, G, NS, 3, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 3, false>(V, pub, nbr, lane); } break;
-    case 4: if constexpr (CAP >= 4) { if (up) exchange_shfl<NG, G, NS, 4, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 4, false>(V, pub, nbr, lane); } break;
-    case 5: if constexpr (CAP >= 5) { if (up) exchange_shfl<NG, G, NS, 5, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 5, false>(V, pub, nbr, lane); } break;
-    case 6: if constexpr (CAP >= 6) { if (up) exchange_shfl<NG, G, NS, 6, true>(V, pub, nbr, lane); else exchange_shfl<NG, G, NS, 6, false>(V, pub, nbr, lane); } break;
+  // one dense switch over (e, direction): a jump table instead of a chain of compares, each of which would be a
+  // possibly divergent branch with its own reconvergence point
+#define NCN_LANE_CASE(EE)                                                                                   \
+  case 2 * EE: if constexpr (CAP >= EE) exchange_shfl<NG, G, NS, EE, false>(V, pub, nbr, lane); break;      \
+  case 2 * EE + 1: if constexpr (CAP >= EE) exchange_shfl<NG, G, NS, EE, true>(V, pub, nbr, lane); break;
+  switch (2 * e + (up ? 1 : 0)) {
+    NCN_LANE_CASE(0)
+    NCN_LANE_CASE(1)
+    NCN_LANE_CASE(2)
+    NCN_LANE_CASE(3)
+    NCN_LANE_CASE(4)
+    NCN_LANE_CASE(5)
+    NCN_LANE_CASE(6)
     default: break;
   }
+#undef NCN_LANE_CASE
 }
 
 // a thread's G*NG contiguous positions of one stream <-> its registers (stride-0 arrangement).
