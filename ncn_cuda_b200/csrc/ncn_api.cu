@@ -496,9 +496,7 @@ static bool lanep_layout(bool bwd, int N, int L, int dtype, int flags, int n_ck,
   const uint64_t RN = (uint64_t)R * N;
   const int threads = R * tpr;
   const int warps = threads / 32;
-  const int kmax = 3 * (e_need >= 0 ? (1 << e_need) : 0);
-  const uint32_t so = (uint32_t)((4 * (kmax + 2) + 7) / 8 * 8);  // bytes per (stream, offset) region
-  pl.halo_warp_bytes = NS * 3 * so;
+  pl.halo_warp_bytes = NS * 3 * kPipeSo;  // a region of kPipeSo bytes per (stream, offset): enough for shifts of 3 * 2^4 blocks
   uint64_t work = NS * RN * w;
   const uint64_t halo = (uint64_t)2 * warps * pl.halo_warp_bytes;  // two half-row "warps" per warp
   if (halo > work) work = halo;

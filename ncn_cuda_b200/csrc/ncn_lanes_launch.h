@@ -39,6 +39,11 @@ __host__ __device__ constexpr int lane_halo_pair_base(int o) {
   return b;
 }
 
+// Pipelined kernels (ncn_lanes_pipe.cuh): bytes between the regions of two (stream, offset) pairs of a warp's halo
+// area: 4 (kmax + 2) for the largest shift they take (kmax = 3 * 16 blocks), a multiple of 16.  A compile-time
+// constant, so that every halo access is "per-thread base register + immediate".
+constexpr unsigned kPipeSo = 208;
+
 // Block size the kernels are compiled for, and the CTAs per SM their register budget allows.
 constexpr int kLaneThreads = 256;
 constexpr int kLaneFwdBlocks = 4;

@@ -31,31 +31,58 @@
 
 namespace ncn {
 
-// byte addresses (shared window) of the halo areas one set of a thread works with
+// byte addresses (shared window) of the halo areas one set of a thread works with, each already advanced to this
+// lane's pair (8 bytes per lane)
 struct PipeHalo {
-  uint32_t mine, up, dn;  // this virtual warp's area; the areas of the warps holding the next higher / lower blocks
-  uint32_t so_stride;     // bytes between the regions of two (stream, offset) pairs
+  uint32_t mine8;  // this virtual warp's area
+  uint32_t up8m;   // the area of the warp holding the next higher blocks, minus 256 (= 32 lanes): lane + q - 32
+  uint32_t dn8;    // the area of the warp holding the next lower blocks
 };
+
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+// predicated shared-memory accesses at [base + IMM]
+template <int IMM>
+__device__ __forceinline__ void sts64_io(bool on, uint32_t a, float x, float y) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.s32 p, %3, 0;\n\t@p st.shared.v2.f32 [%0+%4], {%1, %2};\n\t}" ::"r"(a), "f"(x), "f"(y),
+               "r"((int)on), "n"(IMM)
+               : "memory");
+}
+template <int IMM>
+__device__ __forceinline__ void lds64_io(bool on, uint32_t a, float2& v) {  // v keeps its value where !on
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.s32 p, %3, 0;\n\t@p ld.shared.v2.f32 {%0, %1}, [%2+%4];\n\t}"
+               : "+f"(v.x), "+f"(v.y)
+               : "r"(a), "r"((int)on), "n"(IMM)
+               : "memory");
+}
+template <int IMM>
+__device__ __forceinline__ void lds32_io(bool on, uint32_t a, float& v) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.s32 p, %2, 0;\n\t@p ld.shared.f32 %0, [%1+%3];\n\t}" : "+f"(v) : "r"(a), "r"((int)on), "n"(IMM)
+               : "memory");
+}
 
 // ---- publish: the values the neighbouring warp will want, before this set's registers are shuffled
 // UP = false: consumers take from higher blocks, so a warp publishes its FIRST k values per offset;
 // UP = true: its LAST k values.  k = o * ad (ad = |stride difference|).
 template <int NG, int NS, bool UP>
 __device__ __forceinline__ void pipe_publish(const float2 (&V)[NS][NG], int ad, const PipeHalo& h, int lane) {
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-#pragma unroll
-    for (int o = 1; o < NG; ++o) {
-      const int k = o * ad;
-      const uint32_t reg = h.mine + (uint32_t)(s * (NG - 1) + (o - 1)) * h.so_stride;
-      if (!UP) {
-        sts64_if(2 * lane < k, reg + 8u * (uint32_t)lane, V[s][o].x, V[s][o].y);
-      } else {
-        const int kb = (64 - k) & ~1;  // first published index, rounded down to a pair
-        sts64_if(2 * lane >= kb, reg + 4u * (uint32_t)(2 * lane - kb), V[s][o].x, V[s][o].y);
-      }
+  static_for<0, NS*(NG - 1)>([&](auto ic) {
+    constexpr int idx = decltype(ic)::value;
+    constexpr int s = idx / (NG - 1), o = idx % (NG - 1) + 1;
+    constexpr int OFF = idx * (int)kPipeSo;
+    const int k = o * ad;
+    if (!UP) {
+      sts64_io<OFF>(2 * lane < k, h.mine8, V[s][o].x, V[s][o].y);
+    } else {
+      const int kb = (64 - k) & ~1;  // first published index, rounded down to a pair
+      sts64_io<OFF>(2 * lane >= kb, h.mine8 - 4u * (uint32_t)kb, V[s][o].x, V[s][o].y);
     }
-  }
+  });
 }
 
 // ---- in-warp part of the shift (results for lanes whose source is in another warp are garbage
@@ -94,33 +121,31 @@ __device__ __forceinline__ void pipe_shuffle(float2 (&V)[NS][NG], int ad) {
 // ---- halo part of the shift (after the barrier that follows the neighbours' pipe_publish)
 template <int NG, int NS, bool UP, bool UNIT>
 __device__ __forceinline__ void pipe_fetch(float2 (&V)[NS][NG], int ad, const PipeHalo& h, int lane) {
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-#pragma unroll
-    for (int o = 1; o < NG; ++o) {
-      const uint32_t off = (uint32_t)(s * (NG - 1) + (o - 1)) * h.so_stride;
-      if (UNIT && (o & 1)) {
-        // k = o odd.  down: x <- index 2L + k, y <- 2L + k + 1 of the chunk, minus 64 in the upper warp's halo.
-        //            up:   x <- 2L - k, y <- 2L + 1 - k, plus 64; the lower warp's halo starts at kb = 63 - k.
-        if (!UP) {
-          const int qx = o >> 1, qy = (o + 1) >> 1;
-          lds32_if(lane + qx >= 32, h.up + off + 4u * (uint32_t)(2 * lane + o - 64), V[s][o].x);
-          lds32_if(lane + qy >= 32, h.up + off + 4u * (uint32_t)(2 * lane + o + 1 - 64), V[s][o].y);
-        } else {
-          const int qx = (o + 1) >> 1, qy = o >> 1;
-          lds32_if(lane < qx, h.dn + off + 4u * (uint32_t)(2 * lane + 1), V[s][o].x);
-          lds32_if(lane < qy, h.dn + off + 4u * (uint32_t)(2 * lane + 2), V[s][o].y);
-        }
+  static_for<0, NS*(NG - 1)>([&](auto ic) {
+    constexpr int idx = decltype(ic)::value;
+    constexpr int s = idx / (NG - 1), o = idx % (NG - 1) + 1;
+    constexpr int OFF = idx * (int)kPipeSo;
+    if constexpr (UNIT && (o & 1)) {
+      // k = o odd.  down: x <- index 2L + k, y <- 2L + k + 1 of the chunk, minus 64 in the upper warp's halo.
+      //            up:   x <- 2L - k, y <- 2L + 1 - k, plus 64; the lower warp's halo starts at kb = 63 - k.
+      if (!UP) {
+        constexpr int qx = o >> 1, qy = (o + 1) >> 1;
+        lds32_io<OFF + 4 * o>(lane + qx >= 32, h.up8m, V[s][o].x);
+        lds32_io<OFF + 4 * (o + 1)>(lane + qy >= 32, h.up8m, V[s][o].y);
       } else {
-        const int q = UNIT ? (o >> 1) : (o * ad) >> 1;
-        if (!UP) {
-          lds64_if(lane + q >= 32, h.up + off + 8u * (uint32_t)(lane + q - 32), V[s][o]);
-        } else {
-          lds64_if(lane < q, h.dn + off + 8u * (uint32_t)lane, V[s][o]);
-        }
+        constexpr int qx = (o + 1) >> 1, qy = o >> 1;
+        lds32_io<OFF + 4>(lane < qx, h.dn8, V[s][o].x);
+        lds32_io<OFF + 8>(lane < qy, h.dn8, V[s][o].y);
+      }
+    } else {
+      const int q = UNIT ? (o >> 1) : (o * ad) >> 1;
+      if (!UP) {
+        lds64_io<OFF>(lane + q >= 32, h.up8m + 8u * (uint32_t)q, V[s][o]);
+      } else {
+        lds64_io<OFF>(lane < q, h.dn8, V[s][o]);
       }
     }
-  }
+  });
 }
 
 // Whole shift of both sets with its own barriers (start and end of a tile, where nothing overlaps).
@@ -172,14 +197,13 @@ __device__ __forceinline__ void pipe_st_native(T* chunk, const float2 (&Sv)[NG],
   lane_st_native<NG, 2, T>(chunk, tmp, t);
 }
 
-__device__ __forceinline__ void pipe_halo_init(PipeHalo& h, uint32_t base, uint32_t warp_bytes, uint32_t so_stride, int vw,
-                                               int nvw, int row_first) {
+__device__ __forceinline__ void pipe_halo_init(PipeHalo& h, uint32_t base, uint32_t warp_bytes, int vw, int nvw, int row_first,
+                                               int lane) {
   // vw: virtual warp within the row (0 .. nvw-1, set A first); row_first: first virtual warp of the row in the CTA
   const int up = vw + 1 == nvw ? 0 : vw + 1, dn = vw == 0 ? nvw - 1 : vw - 1;
-  h.mine = base + (uint32_t)(row_first + vw) * warp_bytes;
-  h.up = base + (uint32_t)(row_first + up) * warp_bytes;
-  h.dn = base + (uint32_t)(row_first + dn) * warp_bytes;
-  h.so_stride = so_stride;
+  h.mine8 = base + (uint32_t)(row_first + vw) * warp_bytes + 8u * (uint32_t)lane;
+  h.up8m = base + (uint32_t)(row_first + up) * warp_bytes + 8u * (uint32_t)lane - 256u;
+  h.dn8 = base + (uint32_t)(row_first + dn) * warp_bytes + 8u * (uint32_t)lane;
 }
 
 // ------------------------------------------------------------------------------------------ forward
@@ -226,8 +250,8 @@ __global__ void __launch_bounds__(MAXT, MINB) lanep_fwd_kernel(const LaneParams 
   const int r = tid / TPR, t = tid - r * TPR;  // row of the tile, thread of the row
   const int wpr = TPR >> 5, wr = t >> 5;
   PipeHalo ha, hb;
-  pipe_halo_init(ha, smem_u32(smem + p.off_work), p.halo_warp_bytes, p.halo_warp_bytes / (2 * (NG - 1)), wr, 2 * wpr, r * 2 * wpr);
-  pipe_halo_init(hb, smem_u32(smem + p.off_work), p.halo_warp_bytes, p.halo_warp_bytes / (2 * (NG - 1)), wpr + wr, 2 * wpr, r * 2 * wpr);
+  pipe_halo_init(ha, smem_u32(smem + p.off_work), p.halo_warp_bytes, wr, 2 * wpr, r * 2 * wpr, lane);
+  pipe_halo_init(hb, smem_u32(smem + p.off_work), p.halo_warp_bytes, wpr + wr, 2 * wpr, r * 2 * wpr, lane);
   const int chunkA = r * N + t * (2 * NG);  // set A's positions of the tile; set B's are NH further
   constexpr float sT = (float)F::sT;
   PairW w;
@@ -399,8 +423,8 @@ __global__ void __launch_bounds__(MAXT, MINB) lanep_bwd_kernel(const LaneParams 
   const int r = tid / TPR, t = tid - r * TPR;
   const int wpr = TPR >> 5, wr = t >> 5;
   PipeHalo ha, hb;
-  pipe_halo_init(ha, smem_u32(smem + p.off_work), p.halo_warp_bytes, p.halo_warp_bytes / (4 * (NG - 1)), wr, 2 * wpr, r * 2 * wpr);
-  pipe_halo_init(hb, smem_u32(smem + p.off_work), p.halo_warp_bytes, p.halo_warp_bytes / (4 * (NG - 1)), wpr + wr, 2 * wpr, r * 2 * wpr);
+  pipe_halo_init(ha, smem_u32(smem + p.off_work), p.halo_warp_bytes, wr, 2 * wpr, r * 2 * wpr, lane);
+  pipe_halo_init(hb, smem_u32(smem + p.off_work), p.halo_warp_bytes, wpr + wr, 2 * wpr, r * 2 * wpr, lane);
   const int chunkA = r * N + t * (2 * NG);
   constexpr float sT = (float)F::sT;
   PairWB w;
