@@ -70,9 +70,9 @@ EXTRA_NGPU = ["cfg5"]
 
 # DRAM bytes per element moved by the backward kernel in one launch (dram__bytes_read.sum +
 # dram__bytes_write.sum over B*N) from an ncu capture of the 8192-row case of cfg2 (fp32, one stored
-# state): 831.1 + 267.1 MB over 33.55 M elements.  Traffic grows in proportion to the rows, so the full
+# state): 836.0 + 252.0 MB over 33.55 M elements.  Traffic grows in proportion to the rows, so the full
 # launch is this figure times its elements.
-BWD_TRAFFIC_BYTES_PER_ELEMENT = 32.73
+BWD_TRAFFIC_BYTES_PER_ELEMENT = 32.43
 
 # rows per step of the CPU arms (both the cpu_baseline leg and --impl reference use this one rule)
 CPU_ROWS_PER_STEP = 1024
