@@ -443,7 +443,7 @@ def run_e2e(ncn, wl, dev, dtype, ws, mode, world, rank):
         return {"value": None, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "note": "not measured: pinned host buffers could not be allocated on every rank" + (": " + err if err else "")}
     W = torch.stack([p.detach() for p in ws])
-    reps = 3
+    reps = 5
 
     def one():
         res = net_fwd_bwd_host(hx, hxa, W, hdy, hdya, 0.9, wl["act"], wl["n"], 1, out=out, backward_mode=mode, device=dev)
@@ -479,7 +479,7 @@ def run_e2e(ncn, wl, dev, dtype, ws, mode, world, rank):
     return {"value": world * B / (ms * 1e-3), "unit": "rows/s", "h2d_bytes_per_step": world * 4 * el,
             "d2h_bytes_per_step": world * (4 * el + W.numel() * 4), "rows": world * B, "ms_per_step": ms,
             "wall_ms_per_step": wall * 1e3, "ms_each_repetition": [round(t, 2) for t in times],
-            "note": "host-buffer call (ncn_cuda_b200.host.net_fwd_bwd_host), chunked 3-stream pipeline on every GPU, median of 3 repetitions, max over ranks"}
+            "note": "host-buffer call (ncn_cuda_b200.host.net_fwd_bwd_host), chunked 3-stream pipeline on every GPU, median of 5 repetitions after one warm-up pass, max over ranks"}
 
 
 def main():
