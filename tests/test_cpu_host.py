@@ -35,6 +35,13 @@ def test_library_exports_every_declared_symbol():
     assert loaded.ncn_ckpt_bytes(8, 64, 1, 4, 4, 0) == 0
     assert loaded.ncn_ckpt_bytes(8, 64, 1, 4, 4, 8) == 1 * 2 * 8 * 64 * 4      # tape: the last state
     assert loaded.ncn_ckpt_bytes(8, 64, 1, 6, 4, 8) == 2 * 2 * 8 * 64 * 4
+    # states the per-stage forward stores: one per 16 steps short of the last; with bf16 storage (dtype 1) the end state too
+    one = 2 * 3 * 64 * 128 * 4
+    assert loaded.ncn_stage_mid_bytes(3, 64, 128, 32, 0) == one
+    assert loaded.ncn_stage_mid_bytes(3, 64, 128, 16, 0) == 0
+    assert loaded.ncn_stage_mid_bytes(3, 64, 128, 64, 0) == 3 * one
+    assert loaded.ncn_stage_mid_bytes(3, 64, 128, 16, 1) == one
+    assert loaded.ncn_stage_mid_bytes(3, 64, 128, 32, 1) == 2 * one
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -501,6 +501,21 @@ def test_error_behaviour(ncn):
     with pytest.raises(NCNError) as e:
         ncn.ops.net_fwd(x, x, W.reshape(1, 8), 0.9, 0, 5, 1)  # E != 1: fused path does not apply
     assert e.value.status == 5
+    # the stage forward that stores its states: a missing or short buffer is refused before anything is enqueued
+    from ncn_cuda_b200 import _lib
+
+    lib = _lib.load()
+    xs = torch.randn(2, 64, 8, device="cuda")
+    ys, yas = torch.empty_like(xs), torch.empty_like(xs)
+    Ws = torch.randn(16, device="cuda")
+    need = lib.ncn_stage_mid_bytes(2, 64, 8, 32, 0)
+    mid = torch.empty(need // 4, device="cuda")
+    args = (2, 64, 8, 32, 1, 0, 0.9, 0, 0, torch.cuda.current_stream().cuda_stream)
+    assert lib.ncn_stage_fwd_mid(xs.data_ptr(), xs.data_ptr(), Ws.data_ptr(), ys.data_ptr(), yas.data_ptr(), None, 0, *args) == 8
+    assert lib.ncn_stage_fwd_mid(xs.data_ptr(), xs.data_ptr(), Ws.data_ptr(), ys.data_ptr(), yas.data_ptr(), mid.data_ptr(),
+                                 need - 4, *args) == 6
+    assert lib.ncn_stage_fwd_mid(xs.data_ptr(), xs.data_ptr(), Ws.data_ptr(), ys.data_ptr(), yas.data_ptr(), mid.data_ptr(),
+                                 need, *args) == 0
     ncn.ops.device_status()
 
 
