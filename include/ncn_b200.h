@@ -192,7 +192,10 @@ int ncn_version(void);
 /* The NCN_* environment switches (kernel selection for A/B measurements: NCN_LANES, NCN_LANES_PIPE, NCN_FWD_DUAL, NCN_BWD_DUAL, NCN_NO_PAIR, NCN_NO_FEAT, NCN_EXACT_TANH, ...) are read once,
  * when the library is loaded, and launch plans are remembered per argument set.  This call reads the
  * switches again and forgets the remembered plans.  Not thread-safe against concurrent launches.
- * No counterpart in the reference (which has no such switches). */
+ * No counterpart in the reference (which has no such switches).
+ * The library also remembers, per device, the addresses of its device-side status word and scratch array and the
+ * shared-memory size it has granted each kernel.  cudaDeviceReset() invalidates all of that behind its back: a
+ * process that resets a device must unload and reload the library before using it on that device again. */
 void ncn_reload_env(void);
 
 #ifdef __cplusplus
