@@ -151,15 +151,20 @@ struct LBwdSteps {
 #pragma unroll
     for (int i = 0; i < NG; ++i) ts[i] = ffma2(X[i], Ps, Qs);
     act_r_all<ACT, NG, LaneBatch<NG>::bwd>(ts, r);
-    float2 aI = f2(0.0f), aS = f2(0.0f);
+    float2 aI, aS;  // sums over the group's positions; the first term starts them (no zeroing, no add to zero)
 #pragma unroll
     for (int i = 0; i < NG; ++i) {
       A[i] = ffma2(r[i], f2(cAr), A[i]);
       G[i] = ffma2(f2(kC), H[i], G[i]);
       const float2 gt = F::gt(G[i], ts[i], r[i]);
       H[i] = ffma2(gt, PH, H[i]);
-      aI = ffma2(gt, X[i], aI);
-      aS = fadd2(aS, gt);
+      if (i == 0) {
+        aI = fmul2(gt, X[0]);
+        aS = gt;
+      } else {
+        aI = ffma2(gt, X[i], aI);
+        aS = fadd2(aS, gt);
+      }
     }
     float2 u;
     if constexpr (DX1 != 0.0f) u = ffma2(f2(DX1), aS, aI); else u = aI;  // sum gT x_i = (c ds / m) u
