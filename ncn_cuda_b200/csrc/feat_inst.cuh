@@ -12,18 +12,22 @@ namespace ncn {
 // NCN_MID (without NCN_BWD): the forward that stores the state after every 16th step.
 
 template <int LD, int KF, int ACT, typename T>
-static cudaError_t launch_one(const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
+static cudaError_t launch_one(const FeatParamsX& px, int grid, int threads, cudaStream_t st, int* occ) {
   if constexpr (NCN_NC * LD * KF > 1024) {
     return cudaErrorNotSupported;
   } else {
 #if defined(NCN_BWD) && defined(NCN_SAVED)
-    auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T, true>;
+    auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T, true, FeatParamsX>;
+    const FeatParamsX& p = px;
 #elif defined(NCN_BWD)
     auto k = feat_bwd_kernel<NCN_NC, LD, KF, ACT, T>;
+    const FeatParams p = px;  // the default kernels take the first 128 bytes only
 #elif defined(NCN_MID)
-    auto k = feat_fwd_kernel<NCN_NC, LD, KF, ACT, T, true>;
+    auto k = feat_fwd_kernel<NCN_NC, LD, KF, ACT, T, true, FeatParamsX>;
+    const FeatParamsX& p = px;
 #else
     auto k = feat_fwd_kernel<NCN_NC, LD, KF, ACT, T>;
+    const FeatParams p = px;
 #endif
     if (occ) return cudaOccupancyMaxActiveBlocksPerMultiprocessor(occ, k, threads, 0);
     k<<<grid, threads, 0, st>>>(p);
@@ -32,7 +36,7 @@ static cudaError_t launch_one(const FeatParams& p, int grid, int threads, cudaSt
 }
 
 template <int LD, int KF>
-static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
+static cudaError_t launch_geo(int act, int dtype, const FeatParamsX& p, int grid, int threads, cudaStream_t st, int* occ) {
   if (dtype == DT_F32) {
     switch (act) {
       case ACT_TANH: return launch_one<LD, KF, ACT_TANH, float>(p, grid, threads, st, occ);
@@ -63,7 +67,7 @@ static cudaError_t launch_geo(int act, int dtype, const FeatParams& p, int grid,
 #define NCN_FN NCN_CAT(launch_feat_fwd_n, NCN_NC)
 #endif
 
-cudaError_t NCN_FN(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st, int* occ) {
+cudaError_t NCN_FN(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads, cudaStream_t st, int* occ) {
   switch (d) {
     case 2: return launch_geo<1, 2>(act, dtype, p, grid, threads, st, occ);
     case 4: return launch_geo<1, 4>(act, dtype, p, grid, threads, st, occ);

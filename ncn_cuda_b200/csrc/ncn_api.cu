@@ -722,7 +722,7 @@ static void fill_stage(StageParams& p, int64_t B, int64_t N, int64_t E, int n, i
 }
 
 // ---- register-tiled multi-feature stage kernels (ncn_feat.cuh)
-typedef cudaError_t (*FeatLaunchFn)(int, int, int, const FeatParams&, int, int, cudaStream_t, int*);
+typedef cudaError_t (*FeatLaunchFn)(int, int, int, const FeatParamsX&, int, int, cudaStream_t, int*);
 
 static FeatLaunchFn feat_fn(int n, bool bwd) {
   switch (n) {
@@ -774,7 +774,7 @@ static int launch_feat(bool bwd, const void* const* in, void* const* out, const 
     if (!aligned16(in[q])) return NCN_ERR_UNSUPPORTED;  // (null, where a mode does not read a tensor, counts as aligned)
   for (int q = 0; q < (bwd ? 4 : 2); ++q)
     if (out[q] && !aligned16(out[q])) return NCN_ERR_UNSUPPORTED;
-  FeatParams p{};
+  FeatParamsX p{};
   for (int q = 0; q < 4; ++q) { p.in[q] = in[q]; p.out[q] = out[q]; }
   p.xin[0] = x_saved; p.xin[1] = xa_saved;
   p.saved = saved;

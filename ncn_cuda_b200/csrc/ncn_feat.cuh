@@ -35,20 +35,25 @@ namespace ncn {
 struct FeatParams {
   const void* in[4];  // fwd: x, xa ; bwd: y, ya, dy, dya
   void* out[4];       // fwd: y, ya ; bwd: dx, dxa, x_rec|null, xa_rec|null
-  const void* xin[2]; // bwd with the stage input saved: x, xa
-  int saved;          // bwd: 0 = from the output alone; 1 = the first half of the steps is replayed from
-                      // the saved input; 2 = all steps are (y, ya are not read: bf16 storage); 3 = the states
-                      // the forward stored in `mid` replace the rebuilt ones
-  float* mid;         // fp32 states after every 16th step: state k, stream s at mid + (2k + s) * bne, in the
-                      // element order of the activations (fwd with MID: written; bwd with saved == 3: read)
-  long long bne;      // elements per activation tensor
-  int mid_end;        // the state after the LAST step is stored / read as well (bf16 storage: y, ya are not read)
   const float* W;     // [2E]
   float* partials;    // bwd: [gridDim.x][2E]
   long long B;
   long long units;    // B * mg work units per head
   int N, E, C, m, mg, stride;  // mg = ceil(m / groups per warp)
   float alpha, oma;
+};
+// Parameters of the kernels with a saved stage input or stored states.  A type of its own: the default kernels
+// keep the 128-byte FeatParams (with these fields inside it the default backward, which never reads them, ran
+// 4 % slower: the compiler's schedule at 249 registers is that easily disturbed).
+struct FeatParamsX : FeatParams {
+  const void* xin[2]; // bwd with the stage input saved: x, xa
+  float* mid;         // fp32 states after every 16th step: state k, stream s at mid + (2k + s) * bne, in the
+                      // element order of the activations (fwd with MID: written; bwd with saved == 3: read)
+  long long bne;      // elements per activation tensor
+  int saved;          // bwd: 1 = the first half of the steps is replayed from the saved input; 2 = all steps are
+                      // (y, ya are not read: bf16 storage); 3 = the states the forward stored in `mid` replace
+                      // the rebuilt ones
+  int mid_end;        // the state after the LAST step is stored / read as well (bf16 storage: y, ya are not read)
 };
 
 template <int NC, int LD, int KF>
@@ -118,8 +123,8 @@ __device__ __forceinline__ FeatWarp feat_warp(const FeatParams& p) {
 // ------------------------------------------------------------------------------------------ forward
 // MID: the fp32 state after every 16th step is also written to p.mid, for a backward whose inverse
 // chains then never exceed 16 steps.
-template <int NC, int LD, int KF, int ACT, typename T, bool MID = false>
-__global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatParams p) {
+template <int NC, int LD, int KF, int ACT, typename T, bool MID = false, typename PT = FeatParams>
+__global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const PT p) {
   using G = FeatGeom<NC, LD, KF>;
   using F = ActForm<ACT>;
   constexpr int P = G::P, SEG = G::SEG, KP = G::KP;
@@ -245,8 +250,8 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const FeatPar
 // the state half way is rebuilt exactly by running the forward over the first NC/2 steps from the
 // input, so that no inverse chain is longer than NC/2 steps.  With bf16 storage (p.saved == 2) the
 // end state is replayed too: an inverse started from rounded outputs would amplify their rounding.
-template <int NC, int LD, int KF, int ACT, typename T, bool SAVED = false>
-__global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatParams p) {
+template <int NC, int LD, int KF, int ACT, typename T, bool SAVED = false, typename PT = FeatParams>
+__global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const PT p) {
   using G = FeatGeom<NC, LD, KF>;
   using F = ActForm<ACT>;
   constexpr int P = G::P, SEG = G::SEG, KP = G::KP, D = G::D;
@@ -296,7 +301,9 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const FeatPar
       const int blk = (int)(((long long)g + (long long)i * p.stride) % p.m);
       off[r] = ((b * p.N + (long long)blk * NC + i) * p.E) + fw.c * D + sub * KF;
       if (valid) {
-        if (!(SAVED && (p.saved == 2 || (p.saved == 3 && p.mid_end)))) {
+        bool from_output = true;  // (stored end state or full replay: y, ya are not read)
+        if constexpr (SAVED) from_output = !(p.saved == 2 || (p.saved == 3 && p.mid_end));
+        if (from_output) {
           ld_feat<KF, T>(g_y + off[r], X[r]);
           ld_feat<KF, T>(g_ya + off[r], A[r]);
         }

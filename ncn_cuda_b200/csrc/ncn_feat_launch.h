@@ -6,12 +6,12 @@
 
 namespace ncn {
 
-struct FeatParams;
+struct FeatParamsX;  // FeatParams plus what the kernels with a saved stage input or stored states take
 
 #define NCN_DECL(n)                                                                                          \
-  cudaError_t launch_feat_fwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, int threads,     \
+  cudaError_t launch_feat_fwd_n##n(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads,     \
                                    cudaStream_t st, int* occ);                                                                 \
-  cudaError_t launch_feat_bwd_n##n(int d, int act, int dtype, const FeatParams& p, int grid, int threads,     \
+  cudaError_t launch_feat_bwd_n##n(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads,     \
                                    cudaStream_t st, int* occ);
 NCN_DECL(2)
 NCN_DECL(4)
@@ -20,14 +20,14 @@ NCN_DECL(16)
 NCN_DECL(32)
 #undef NCN_DECL
 // the backward that also takes the saved stage input (inverse chains of n_cache / 2 steps)
-cudaError_t launch_feat_bwds_n16(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+cudaError_t launch_feat_bwds_n16(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads, cudaStream_t st,
                                  int* occ);
-cudaError_t launch_feat_bwds_n32(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+cudaError_t launch_feat_bwds_n32(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads, cudaStream_t st,
                                  int* occ);
 // the forward that also stores the state after every 16th step
-cudaError_t launch_feat_fwdm_n16(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+cudaError_t launch_feat_fwdm_n16(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads, cudaStream_t st,
                                  int* occ);
-cudaError_t launch_feat_fwdm_n32(int d, int act, int dtype, const FeatParams& p, int grid, int threads, cudaStream_t st,
+cudaError_t launch_feat_fwdm_n32(int d, int act, int dtype, const FeatParamsX& p, int grid, int threads, cudaStream_t st,
                                  int* occ);
 
 // groups a warp works on side by side for (n_cache, d); 0 if there is no kernel
