@@ -309,6 +309,14 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const PT p) {
         }
         ld_feat<KF, T>(g_dy + off[r], H[r]);
         ld_feat<KF, T>(g_dya + off[r], Gv[r]);
+        if constexpr (SAVED) {
+          // the stored state is needed half a stage from now: towards L2 already (one lane per 128-byte line)
+          if (p.saved == 3 && (sub & (128 / (KF * 4) - 1)) == 0) {
+            const float* mx = p.mid + off[r];
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(mx));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(mx + p.bne));
+          }
+        }
       } else {
 #pragma unroll
         for (int q = 0; q < KP; ++q) X[r][q] = A[r][q] = H[r][q] = Gv[r][q] = f2(0.0f);
