@@ -156,7 +156,7 @@ int ncn_net_bwd(const void* s0, const void* s1, const void* dy, const void* dya,
  *    beyond it the call returns NCN_ERR_TOO_LARGE and enqueues nothing.
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
- *    that device current); make that first call outside any stream capture.
+ *    that device current).
  *  - All calls on a device share the one array and it keeps the last call's partial sums.  Nothing
  *    in it has to be cleared (the kernel writes every element the reduction reads), but two calls
  *    whose kernels overlap on the GPU (different streams, no ordering) race on it: order them. */
