@@ -172,6 +172,18 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const PT p) {
         for (int q = 0; q < KP; ++q) X[r][q] = A[r][q] = f2(0.0f);
       }
     }
+    [[maybe_unused]] auto store_mid = [&](int done) {  // the state after `done` steps, for the backward (MID)
+      if constexpr (MID) {
+        if (valid) {
+          float* mx = p.mid + (long long)(2 * (done / 16 - 1)) * p.bne;
+#pragma unroll
+          for (int r = 0; r < P; ++r) {
+            st_feat<KF, float>(mx + off[r], X[r]);
+            st_feat<KF, float>(mx + p.bne + off[r], A[r]);
+          }
+        }
+      }
+    };
 #pragma unroll
     for (int rj = 0; rj < P; ++rj) {
 #pragma unroll 1
@@ -208,17 +220,14 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_fwd_kernel(const PT p) {
             X[r][q] = __ffma2_rn(A[r][q], f2(kC), __fmul2_rn(X[r][q], f2(kM)));
           }
         }
-        if constexpr (MID) {
-          const int done = rj * SEG + sj + 1;  // steps taken
-          if ((done & 15) == 0 && (done < NC || p.mid_end) && valid) {
-            float* mx = p.mid + (long long)(2 * (done / 16 - 1)) * p.bne;
-#pragma unroll
-            for (int r = 0; r < P; ++r) {
-              st_feat<KF, float>(mx + off[r], X[r]);
-              st_feat<KF, float>(mx + p.bne + off[r], A[r]);
-            }
-          }
+        if constexpr (MID && SEG > 16) {  // a boundary of 16 steps inside this run of SEG steps
+          const int done = rj * SEG + sj + 1;
+          if ((done & 15) == 0 && (done < NC || p.mid_end)) store_mid(done);
         }
+      }
+      if constexpr (MID && SEG <= 16) {  // boundaries of 16 steps fall between two runs (rj is unrolled: known at compile time)
+        const int done = (rj + 1) * SEG;
+        if ((done & 15) == 0 && (done < NC || p.mid_end)) store_mid(done);
       }
     }
     if (valid) {
