@@ -331,11 +331,13 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const PT p) {
         for (int q = 0; q < KP; ++q) X[r][q] = A[r][q] = H[r][q] = Gv[r][q] = f2(0.0f);
       }
     }
-#pragma unroll kFeatBwdUnroll
-    for (int j = NC - 1; j >= 0; --j) {
-      // one body for every step: the row index of x_j inside a lane (rj) is a run-time value,
-      // resolved by selects, so that the code stays small enough for the instruction cache
+    // SAVED: the steps go in two runs of NC / 2; what replaces the rebuilt state (stored by the forward, or replayed
+    // from the saved input) is dealt with between the runs, outside the step loop.  Otherwise one run of NC steps.
+    constexpr int RUN = SAVED ? NC / 2 : NC;
+#pragma unroll 1
+    for (int j0 = NC - 1; j0 >= 0; j0 -= RUN) {
       if constexpr (SAVED) {
+        const int j = j0;  // the state wanted is the one after step j0
         if (p.saved == 3) {
           // the state after step j as the forward stored it
           if (((j + 1) & 15) == 0 && (j + 1 < NC || p.mid_end) && valid) {
@@ -389,6 +391,10 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const PT p) {
           }
         }
       }
+#pragma unroll kFeatBwdUnroll
+    for (int j = j0; j > j0 - RUN; --j) {
+      // one body for every step: the row index of x_j inside a lane (rj) is a run-time value,
+      // resolved by selects, so that the code stays small enough for the instruction cache
       const int rj = j / SEG, sj = j - rj * SEG;
       const int src = (gw * SEG + sj) * LD + sub;
       const bool is_j = (s == sj);
@@ -495,6 +501,7 @@ __global__ void __launch_bounds__(kFeatWarps * 32) feat_bwd_kernel(const PT p) {
         if (is_j) dwj[q] = __ffma2_rn(f2(S), xj[q], dwj[q]);
       }
     }
+    }  // runs
     if (valid) {
 #pragma unroll
       for (int r = 0; r < P; ++r) {
